@@ -195,3 +195,177 @@ def _merge_generation_eos(model_dir: str, d: Dict[str, Any]) -> None:
     if not all(isinstance(t, int) and not isinstance(t, bool) for t in merged):
         raise ConfigError(f"{path}: eos_token_id must be an integer or a list of integers")
     d["eos_token_id"] = merged if len(merged) != 1 else merged[0]
+
+
+# ---------------------------------------------------------------- Dobedra
+
+def _section(d: Dict[str, Any], key: str, where: str, optional: bool = False) -> Optional[Dict[str, Any]]:
+    v = d.get(key)
+    if v is None:
+        if optional:
+            return None
+        raise ConfigError(f"config.json: {where}missing section '{key}'")
+    if not isinstance(v, dict):
+        raise ConfigError(f"config.json: {where}'{key}' must be an object")
+    return v
+
+
+@dataclass(frozen=True)
+class LatentAttentionSizes:
+    """One ``latent_attention`` mixer: ``heads`` heads of ``dim`` unrotated + ``rot_dim`` rotated query/key
+    elements and ``vdim`` value elements over a key/value latent of ``kv_rank`` (queries through one of
+    ``q_rank``); ``kv_from``: the layer whose latent cache this one reads instead of keeping one."""
+    heads: int
+    dim: int
+    rot_dim: int
+    vdim: int
+    kv_rank: int
+    q_rank: int
+    scale: float
+    rot_base: float
+    rot_dims: int
+    kv_from: Optional[int] = None
+
+    @classmethod
+    def from_dict(cls, m: Dict[str, Any], where: str) -> "LatentAttentionSizes":
+        rot = _section(m, "rot", where)
+        s = cls(heads=_take(m, "heads", int), dim=_take(m, "dim", int), rot_dim=_take(m, "rot_dim", int),
+                vdim=_take(m, "vdim", int), kv_rank=_take(m, "kv_rank", int), q_rank=_take(m, "q_rank", int),
+                scale=_take(m, "scale", float), rot_base=_take(rot, "base", float),
+                rot_dims=_take(rot, "dims", int), kv_from=_take(m, "kv_from", int, None))
+        for f in ("heads", "dim", "rot_dim", "vdim", "kv_rank", "q_rank"):
+            if getattr(s, f) <= 0:
+                raise ConfigError(f"config.json: {where}'{f}' must be positive, got {getattr(s, f)}")
+        if s.rot_dims <= 0 or s.rot_dims % 2 or s.rot_dims > s.rot_dim:
+            raise ConfigError(f"config.json: {where}rot.dims {s.rot_dims} must be even and at most rot_dim {s.rot_dim}")
+        if not s.rot_base > 0:
+            raise ConfigError(f"config.json: {where}rot.base must be positive")
+        return s
+
+
+@dataclass(frozen=True)
+class FeedForwardSizes:
+    """``kind`` "dense" (gated, ``ff`` wide) or "moe" (``experts`` experts ``ff`` wide of which a token uses
+    ``top``; ``shared_ff`` > 0: a shared expert of that width runs for every token)."""
+    kind: str
+    ff: int
+    experts: int = 0
+    top: int = 0
+    shared_ff: int = 0
+
+    @classmethod
+    def from_dict(cls, m: Dict[str, Any], where: str) -> "FeedForwardSizes":
+        kind = _take(m, "kind", str)
+        if kind == "dense":
+            s = cls("dense", _take(m, "ff", int))
+        elif kind == "moe":
+            router = _section(m, "router", where)
+            shared = _section(m, "shared", where, optional=True)
+            s = cls("moe", _take(_section(m, "expert", where), "ff", int), experts=_take(router, "experts", int),
+                    top=_take(router, "top", int), shared_ff=_take(shared, "ff", int) if shared else 0)
+            if not (0 < s.top <= s.experts):
+                raise ConfigError(f"config.json: {where}router.top {s.top} must be between 1 and experts {s.experts}")
+            if s.shared_ff < 0:
+                raise ConfigError(f"config.json: {where}shared.ff must not be negative")
+        else:
+            raise ConfigError(f"config.json: {where}unknown mlp.kind {kind!r} (dense, moe)")
+        if s.ff <= 0:
+            raise ConfigError(f"config.json: {where}ff must be positive, got {s.ff}")
+        return s
+
+
+@dataclass(frozen=True)
+class DobedraLayer:
+    type: str
+    mixer: LatentAttentionSizes
+    mlp: Optional[FeedForwardSizes]
+
+
+@dataclass(frozen=True)
+class DobedraConfig:
+    """``config.json`` of a Dobedra model: ``vocab``, ``width``, ``norm.eps``, ``logit_softcap`` and the list
+    ``layers``, each entry with its ``type`` (the mixer it has), the mixer's sizes and its feed-forward (or none).
+    ``max_positions`` is optional: the design has no longest sequence of its own, the engine's ``max_model_len``
+    sizes the angle tables."""
+    vocab: int
+    width: int
+    norm_eps: float
+    logit_softcap: float
+    layers: Tuple[DobedraLayer, ...]
+    max_positions: int = 1 << 20
+    eos_token_ids: Tuple[int, ...] = ()
+    architecture: str = "Dobedra"
+
+    MIXER_TYPES = ("latent_attention",)
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "DobedraConfig":
+        raw = d.get("layers")
+        if not isinstance(raw, list) or not raw:
+            raise ConfigError("config.json: 'layers' must be a non-empty list")
+        layers = []
+        for i, l in enumerate(raw):
+            where = f"layers[{i}]: "
+            if not isinstance(l, dict):
+                raise ConfigError(f"config.json: {where}must be an object")
+            kind = _take(l, "type", str)
+            if kind not in cls.MIXER_TYPES:
+                raise ConfigError(f"config.json: {where}unknown type {kind!r} ({', '.join(cls.MIXER_TYPES)})")
+            mixer = LatentAttentionSizes.from_dict(_section(l, "mixer", where), where)
+            mlp = _section(l, "mlp", where, optional=True)
+            layers.append(DobedraLayer(kind, mixer, FeedForwardSizes.from_dict(mlp, where) if mlp else None))
+        eos = d.get("eos_token_id")
+        eos_ids = (eos,) if isinstance(eos, int) and not isinstance(eos, bool) else \
+            tuple(int(x) for x in eos) if isinstance(eos, (list, tuple)) else ()
+        cfg = cls(vocab=_take(d, "vocab", int), width=_take(d, "width", int),
+                  norm_eps=_take(_section(d, "norm", ""), "eps", float),
+                  logit_softcap=_take(d, "logit_softcap", float, 0.0), layers=tuple(layers),
+                  max_positions=_take(d, "max_positions", int, 1 << 20), eos_token_ids=eos_ids,
+                  architecture=str(d.get("architecture") or (d.get("architectures") or ["Dobedra"])[0]))
+        cfg.check()
+        return cfg
+
+    def check(self) -> None:
+        if self.vocab <= 0 or self.width <= 0 or self.max_positions <= 1:
+            raise ConfigError("config.json: vocab, width and max_positions must be positive")
+        if not self.norm_eps > 0:
+            raise ConfigError(f"config.json: norm.eps must be positive, got {self.norm_eps}")
+        if self.logit_softcap < 0:
+            raise ConfigError("config.json: logit_softcap must not be negative")
+        for i, l in enumerate(self.layers):
+            j = l.mixer.kv_from
+            if j is None:
+                continue
+            if not (0 <= j < i) or self.layers[j].mixer.kv_from is not None:
+                raise ConfigError(f"config.json: layers[{i}]: kv_from {j} must name an earlier layer that has a "
+                                  f"key/value down projection of its own")
+            a, b = l.mixer, self.layers[j].mixer
+            if (a.kv_rank, a.rot_dim, a.rot_dims, a.rot_base) != (b.kv_rank, b.rot_dim, b.rot_dims, b.rot_base):
+                raise ConfigError(f"config.json: layers[{i}]: kv_rank, rot_dim and rotation must equal those of "
+                                  f"layer {j}, whose latents it reads")
+
+    def to_dict(self) -> Dict[str, Any]:
+        layers = []
+        for l in self.layers:
+            m = l.mixer
+            mixer = {"heads": m.heads, "dim": m.dim, "rot_dim": m.rot_dim, "vdim": m.vdim, "kv_rank": m.kv_rank,
+                     "q_rank": m.q_rank, "scale": m.scale, "rot": {"base": m.rot_base, "dims": m.rot_dims}}
+            if m.kv_from is not None:
+                mixer["kv_from"] = m.kv_from
+            f = l.mlp
+            if f is None:
+                mlp = None
+            elif f.kind == "dense":
+                mlp = {"kind": "dense", "ff": f.ff}
+            else:
+                mlp = {"kind": "moe", "expert": {"ff": f.ff}, "router": {"experts": f.experts, "top": f.top}}
+                if f.shared_ff:
+                    mlp["shared"] = {"ff": f.shared_ff}
+            layers.append({"type": l.type, "mixer": mixer, "mlp": mlp})
+        d = {"architecture": self.architecture, "vocab": self.vocab, "width": self.width,
+             "norm": {"eps": self.norm_eps}, "logit_softcap": self.logit_softcap, "layers": layers}
+        if self.max_positions != 1 << 20:
+            d["max_positions"] = self.max_positions
+        if self.eos_token_ids:
+            d["eos_token_id"] = list(self.eos_token_ids)
+        return d

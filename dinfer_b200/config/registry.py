@@ -1,4 +1,4 @@
-"""One registry from an architecture's name (``config.json``'s ``architectures[0]``) to the
+"""One registry from an architecture's name (``config.json``'s ``architectures[0]``, or its ``architecture``) to the
 pair that makes a model of it: the typed configuration and the function that turns that
 configuration into a ``ModelSpec`` (the list of layers and parts).
 
@@ -44,8 +44,11 @@ def resolve_architecture(config_dict: Dict[str, Any]) -> Architecture:
     """The registered architecture that ``config.json`` names."""
     _ensure_builtin()
     archs = config_dict.get("architectures")
+    if archs is None and isinstance(config_dict.get("architecture"), str):
+        archs = [config_dict["architecture"]]               # files that name their one design by a plain string
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config.json: 'architectures' must be a non-empty list of names")
+        raise ConfigError("config.json: 'architectures' must be a non-empty list of names "
+                          "(or 'architecture' one name)")
     name = archs[0]
     if name not in _ARCHITECTURES:
         raise ConfigError(
@@ -61,4 +64,4 @@ def _ensure_builtin() -> None:
     global _builtin_loaded
     if not _builtin_loaded:
         _builtin_loaded = True
-        from ..models import qwen3  # noqa: F401  (registers itself)
+        from ..models import dobedra, qwen3  # noqa: F401  (register themselves)

@@ -38,6 +38,9 @@ LIBRARIES: Dict[str, tuple] = {
     "gemm_tc": ("gemm_tc.cu", []),
     "attention_umma": ("attention_umma.cu", []),
     "attention_umma64": ("attention_umma64.cu", []),
+    "latent_post": ("latent_post.cu", []),
+    "attention_latent": ("attention_latent.cu", []),
+    "moe": ("moe.cu", []),
     # host-side bookkeeping (page pools, cache manager, decode plans): plain C++, no CUDA
     "host_core": ("host_core.cpp", []),
 }

@@ -44,6 +44,29 @@ __global__ void silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, in
   }
 }
 
+// out[t, i] = act(gate_i) * up_i for the gates that are not silu (1: the tanh form of gelu, 2: relu, 3: relu
+// squared), same layouts as silu_mul; 32-bit arithmetic, one rounding
+__device__ __forceinline__ float gate_activation(float z, int act) {
+  switch (act) {
+    case 1: return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    case 2: return fmaxf(z, 0.f);
+    case 3: { const float r = fmaxf(z, 0.f); return r * r; }
+    default: return z / (1.f + expf(-z));
+  }
+}
+template <typename T>
+__global__ void gated_act_kernel(const T* __restrict__ x, T* __restrict__ out, int inter, int64_t ldx, int pairs, int act) {
+  pdl_enter();
+  const int t = blockIdx.x;
+  const T* row = x + (int64_t)t * ldx;
+  T* o = out + (int64_t)t * inter;
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < inter; i += gridDim.y * blockDim.x) {
+    const float a = to_f32<T>(pairs ? row[2 * i] : row[i]);
+    const float b = to_f32<T>(pairs ? row[2 * i + 1] : row[inter + i]);
+    o[i] = from_f32<T>(gate_activation(a, act) * b);
+  }
+}
+
 // out[t, n] += bias[n]: the bias of a linear part (none of the Qwen3 dense model's products has one; a mixer
 // or feed-forward of another architecture may), added in 32-bit with one rounding
 template <typename T, typename TB>
@@ -196,5 +219,21 @@ DINFER_API int dinfer_add_bias(void* out, int64_t ld, const void* bias, int T, i
       launch_pdl(add_bias_kernel<TA, TB>, grid, dim3(256), 0, stream, (TA*)out, ld, (const TB*)bias, N);
       return cuda_status("add_bias");
     }));
+  return 0;
+}
+
+// x [T, 2*inter] with row stride ldx; out [T, inter]; act 0 silu, 1 tanh-gelu, 2 relu, 3 relu squared.
+DINFER_API int dinfer_gated_act(const void* x, void* out, int T, int inter, int64_t ldx, int dtype, int pairs, int act,
+                                cudaStream_t stream) {
+  if (act == 0) return dinfer_silu_mul(x, out, T, inter, ldx, dtype, pairs, stream);
+  if (T < 0 || inter <= 0 || ldx < 2 * (int64_t)inter || act < 0 || act > 3)
+    return refuse(DINFER_BAD_ARGUMENT, "gated_act: bad arguments T=%d inter=%d ldx=%lld act=%d", T, inter, (long long)ldx, act);
+  if (T == 0) return 0;
+  int by = (inter + 255) / 256;
+  if (by > 64) by = 64;
+  DINFER_DISPATCH_DTYPE(dtype, T_, {
+    launch_pdl(gated_act_kernel<T_>, dim3(T, by), dim3(256), 0, stream, (const T_*)x, (T_*)out, inter, ldx, pairs, act);
+    return cuda_status("gated_act");
+  });
   return 0;
 }

@@ -17,7 +17,8 @@ constexpr int BM = 128, BN = 128, BK = 8;
 template <typename TA, typename TW, typename TC>
 __global__ void __launch_bounds__(256)
 gemm_tile_kernel(const TA* __restrict__ A, int64_t lda, const TW* __restrict__ W, int64_t ldw,
-                 TC* __restrict__ C, int64_t ldc, int M, int N, int K) {
+                 TC* __restrict__ C, int64_t ldc, int M, int N, int K, int64_t sa, int64_t sw, int64_t sc) {
+  A += (int64_t)blockIdx.z * sa; W += (int64_t)blockIdx.z * sw; C += (int64_t)blockIdx.z * sc;
   __shared__ float As[BK][BM];
   __shared__ float Ws[BK][BN];
   const int tid = threadIdx.x;
@@ -69,7 +70,8 @@ gemm_tile_kernel(const TA* __restrict__ A, int64_t lda, const TW* __restrict__ W
 template <typename TA, typename TW, typename TC, int ROWS>
 __global__ void __launch_bounds__(256)
 gemm_rows_kernel(const TA* __restrict__ A, int64_t lda, const TW* __restrict__ W, int64_t ldw,
-                 TC* __restrict__ C, int64_t ldc, int M, int N, int K) {
+                 TC* __restrict__ C, int64_t ldc, int M, int N, int K, int64_t sa, int64_t sw, int64_t sc) {
+  A += (int64_t)blockIdx.z * sa; W += (int64_t)blockIdx.z * sw; C += (int64_t)blockIdx.z * sc;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = blockIdx.x * 8 + warp;
   if (n >= N) return;
@@ -92,15 +94,16 @@ gemm_rows_kernel(const TA* __restrict__ A, int64_t lda, const TW* __restrict__ W
 
 template <typename TA, typename TW, typename TC>
 int launch(const void* A, int64_t lda, const void* W, int64_t ldw, void* C, int64_t ldc, int M, int N,
-           int K, cudaStream_t stream) {
+           int K, cudaStream_t stream, int batch = 1, int64_t sa = 0, int64_t sw = 0, int64_t sc = 0) {
+  if (batch > 65535) return refuse(DINFER_BAD_ARGUMENT, "gemm_f32: batch=%d too large", batch);
   if (M <= 8) {
-    gemm_rows_kernel<TA, TW, TC, 8><<<(N + 7) / 8, 256, 0, stream>>>(
-        (const TA*)A, lda, (const TW*)W, ldw, (TC*)C, ldc, M, N, K);
+    gemm_rows_kernel<TA, TW, TC, 8><<<dim3((N + 7) / 8, 1, batch), 256, 0, stream>>>(
+        (const TA*)A, lda, (const TW*)W, ldw, (TC*)C, ldc, M, N, K, sa, sw, sc);
   } else {
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
     if (grid.y > 65535) return refuse(DINFER_BAD_ARGUMENT, "gemm_f32: M=%d too large", M);
     gemm_tile_kernel<TA, TW, TC><<<grid, 256, 0, stream>>>(
-        (const TA*)A, lda, (const TW*)W, ldw, (TC*)C, ldc, M, N, K);
+        (const TA*)A, lda, (const TW*)W, ldw, (TC*)C, ldc, M, N, K, sa, sw, sc);
   }
   return cuda_status("gemm_f32");
 }
@@ -121,5 +124,21 @@ DINFER_API int dinfer_gemm_f32(const void* A, int64_t lda, int a_dtype, const vo
     DINFER_DISPATCH_DTYPE(w_dtype, TW,
       DINFER_DISPATCH_DTYPE(c_dtype, TC,
         return launch<TA, TW, TC>(A, lda, W, ldw, C, ldc, M, N, K, stream))));
+  return 0;
+}
+
+// The same product for `batch` independent problems: problem b reads A + b * sa, W + b * sw and writes C + b * sc
+// (strides in elements; the problems of a batch may interleave inside one tensor, e.g. the heads of a row).
+DINFER_API int dinfer_gemm_f32_batched(const void* A, int64_t lda, int64_t sa, int a_dtype, const void* W, int64_t ldw,
+                                       int64_t sw, int w_dtype, void* C, int64_t ldc, int64_t sc, int c_dtype, int M,
+                                       int N, int K, int batch, cudaStream_t stream) {
+  if (M < 0 || N <= 0 || K <= 0 || batch <= 0 || lda < K || ldw < K || ldc < N)
+    return refuse(DINFER_BAD_ARGUMENT, "gemm_f32_batched: bad sizes M=%d N=%d K=%d batch=%d lda=%lld ldw=%lld ldc=%lld",
+                  M, N, K, batch, (long long)lda, (long long)ldw, (long long)ldc);
+  if (M == 0) return 0;
+  DINFER_DISPATCH_DTYPE(a_dtype, TA,
+    DINFER_DISPATCH_DTYPE(w_dtype, TW,
+      DINFER_DISPATCH_DTYPE(c_dtype, TC,
+        return launch<TA, TW, TC>(A, lda, W, ldw, C, ldc, M, N, K, stream, batch, sa, sw, sc))));
   return 0;
 }

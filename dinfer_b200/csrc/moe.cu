@@ -1,0 +1,319 @@
+// A routed feed-forward (mixture of experts), as five kernels that never meet the host between them:
+//
+//   moe_router     per token: 32-bit router logits z = W_r h, scores (softmax over all experts, or a sigmoid each),
+//                  the `top` largest scores (ties to the lower index) -> expert ids and weights (the scores, or
+//                  the scores divided by their sum); optionally the gate of a shared expert, sigmoid(w_g . h)
+//   moe_align      the (token, choice) pairs counted per expert and laid out expert by expert, each expert's run
+//                  padded to a multiple of the row tile, so that a row tile belongs to one expert
+//   moe_gemm       grouped product over those tiles: rows gathered by pair (first product, an activation in the
+//                  epilogue) or read in place (second product, each row times its routing weight, scattered
+//                  back to its pair)
+//   moe_combine    out[t] = sum over the token's choices, in the order of the choices (+ gate * shared expert)
+//
+// A pair's row depends on nothing but its token and expert: where it lands inside a tile, and what else is in
+// the batch, changes no bit of it.  Router, scores, weights and the gate are 32-bit; products accumulate in 32-bit.
+#include "common.cuh"
+
+using namespace dinfer;
+
+namespace {
+
+enum Act : int { ACT_NONE = 0, ACT_RELU2 = 1, ACT_SILU = 2, ACT_GELU_TANH = 3, ACT_RELU = 4 };
+
+__device__ __forceinline__ float activate(float z, int act) {
+  switch (act) {
+    case ACT_RELU2: { const float r = fmaxf(z, 0.f); return r * r; }
+    case ACT_RELU: return fmaxf(z, 0.f);
+    case ACT_SILU: return z / (1.f + expf(-z));
+    case ACT_GELU_TANH: return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    default: return z;
+  }
+}
+
+// ---------------------------------------------------------------- router
+constexpr int RW = 4;   // warps (tokens) per block
+
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(RW * 32)
+moe_router_kernel(const TA* __restrict__ h, int64_t ldh, const TW* __restrict__ wr, const TW* __restrict__ wg,
+                  int* __restrict__ ids, float* __restrict__ weights, float* __restrict__ gate, int T, int K, int E,
+                  int top, int sigmoid_scores, int renorm) {
+  extern __shared__ float sm[];                          // RW * E scores
+  pdl_enter();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * RW + warp;
+  if (t >= T) return;
+  float* z = sm + warp * E;
+  const TA* x = h + (int64_t)t * ldh;
+  for (int e = 0; e < E; ++e) {
+    const TW* w = wr + (int64_t)e * K;
+    float a = 0.f;
+    for (int k = lane; k < K; k += 32) a = fmaf(to_f32<TA>(x[k]), to_f32<TW>(w[k]), a);
+    a = warp_sum(a);
+    if (lane == 0) z[e] = a;
+  }
+  if (wg && gate) {
+    float a = 0.f;
+    for (int k = lane; k < K; k += 32) a = fmaf(to_f32<TA>(x[k]), to_f32<TW>(wg[k]), a);
+    a = warp_sum(a);
+    if (lane == 0) gate[t] = 1.f / (1.f + expf(-a));
+  }
+  __syncwarp();
+  if (sigmoid_scores) {
+    for (int e = lane; e < E; e += 32) z[e] = 1.f / (1.f + expf(-z[e]));
+  } else {
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) { const float p = expf(z[e] - mx); z[e] = p; sum += p; }
+    sum = warp_sum(sum);
+    const float inv = 1.f / sum;
+    for (int e = lane; e < E; e += 32) z[e] *= inv;
+  }
+  __syncwarp();
+  float chosen_sum = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int arg = E;
+    for (int e = lane; e < E; e += 32) {
+      const float v = z[e];
+      if (v > best) { best = v; arg = e; }               // the lowest index of a lane's equal scores stays
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+    }
+    if (lane == 0) {
+      ids[(int64_t)t * top + k] = arg;
+      weights[(int64_t)t * top + k] = best;
+      z[arg] = -INFINITY;
+    }
+    chosen_sum += best;
+    __syncwarp();
+  }
+  if (renorm && lane == 0) {
+    const float inv = 1.f / chosen_sum;
+    for (int k = 0; k < top; ++k) weights[(int64_t)t * top + k] *= inv;
+  }
+}
+
+// ---------------------------------------------------------------- pairs laid out expert by expert
+// sorted[pos] = pair index (t * top + k) or `pairs` for padding; tile_expert[tile] = expert of the tile or -1
+__global__ void __launch_bounds__(1024)
+moe_align_kernel(const int* __restrict__ ids, int* __restrict__ sorted, int* __restrict__ tile_expert, int pairs,
+                 int E, int BM, int cap, int max_tiles) {
+  extern __shared__ int smi[];                            // count[E], start[E + 1], fill[E]
+  int* count = smi;
+  int* start = smi + E;
+  int* fill = smi + 2 * E + 1;
+  pdl_enter();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) { count[e] = 0; fill[e] = 0; }
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    const int e = ids[i];
+    if (e >= 0 && e < E) atomicAdd(&count[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0;
+    for (int e = 0; e < E; ++e) { start[e] = at; at += (count[e] + BM - 1) / BM * BM; }
+    start[E] = at;
+  }
+  __syncthreads();
+  const int used = start[E];
+  for (int i = threadIdx.x; i < cap; i += blockDim.x) sorted[i] = pairs;
+  for (int tile = threadIdx.x; tile < max_tiles; tile += blockDim.x) {
+    const int row = tile * BM;
+    int e = -1;
+    if (row < used) {                                     // the expert whose padded run holds this row
+      int lo = 0, hi = E - 1;
+      while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (start[mid] <= row) lo = mid; else hi = mid - 1; }
+      e = lo;
+    }
+    tile_expert[tile] = e;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    const int e = ids[i];
+    if (e >= 0 && e < E) sorted[start[e] + atomicAdd(&fill[e], 1)] = i;
+  }
+}
+
+// ---------------------------------------------------------------- grouped product, plain arithmetic
+// Tile BM rows x 64 columns, 256 threads, K in steps of 16.  MODE 0: A rows gathered from h by pair / top, output
+// row = position, epilogue = activation.  MODE 1: A rows = positions, output row = pair, epilogue = times weight.
+template <typename TA, typename TW, int BM, int MODE>
+__global__ void __launch_bounds__(256)
+moe_gemm_simt_kernel(const TA* __restrict__ A, int64_t lda, const TW* __restrict__ Wall, TA* __restrict__ C,
+                     int64_t ldc, const int* __restrict__ sorted, const int* __restrict__ tile_expert,
+                     const float* __restrict__ weights, int pairs, int top, int N, int K, int act) {
+  constexpr int BN = 64, BK = 16, RPT = BM / 16;          // rows per thread
+  __shared__ float As[BK][BM + 1];
+  __shared__ float Ws[BK][BN + 1];
+  __shared__ int64_t src[BM];
+  __shared__ int pair_of[BM];
+  pdl_enter();
+  const int tile = blockIdx.y;
+  const int e = tile_expert[tile];
+  if (e < 0) return;
+  const int n0 = blockIdx.x * BN;
+  const int tid = threadIdx.x;
+  if (tid < BM) {
+    const int p = sorted[tile * BM + tid];
+    pair_of[tid] = p;
+    src[tid] = p >= pairs ? -1 : (MODE == 0 ? (int64_t)(p / top) * lda : (int64_t)(tile * BM + tid) * lda);
+  }
+  __syncthreads();
+  const TW* W = Wall + (int64_t)e * N * K;
+  const int tx = tid & 15, ty = tid >> 4;
+  float acc[RPT][4];
+#pragma unroll
+  for (int i = 0; i < RPT; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += BK) {
+    for (int i = tid; i < BM * BK; i += 256) {
+      const int r = i / BK, k = i % BK;
+      As[k][r] = (src[r] >= 0 && k0 + k < K) ? to_f32<TA>(A[src[r] + k0 + k]) : 0.f;
+    }
+    for (int i = tid; i < BN * BK; i += 256) {
+      const int n = i / BK, k = i % BK;
+      Ws[k][n] = (n0 + n < N && k0 + k < K) ? to_f32<TW>(W[(int64_t)(n0 + n) * K + k0 + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < BK; ++k) {
+      float a[RPT], b[4];
+#pragma unroll
+      for (int i = 0; i < RPT; ++i) a[i] = As[k][ty + 16 * i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Ws[k][tx + 16 * j];
+#pragma unroll
+      for (int i = 0; i < RPT; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < RPT; ++i) {
+    const int r = ty + 16 * i;
+    const int p = pair_of[r];
+    if (p >= pairs) continue;
+    const int64_t row = MODE == 0 ? (int64_t)(tile * BM + r) : (int64_t)p;
+    const float w = MODE == 1 ? weights[p] : 1.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx + 16 * j;
+      if (n < N) C[row * ldc + n] = from_f32<TA>(MODE == 0 ? activate(acc[i][j], act) : acc[i][j] * w);
+    }
+  }
+}
+
+// ---------------------------------------------------------------- combine
+template <typename TA>
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const TA* __restrict__ y, const TA* __restrict__ shared, const float* __restrict__ gate,
+                   TA* __restrict__ out, int top, int h) {
+  pdl_enter();
+  const int t = blockIdx.x;
+  const float g = gate ? gate[t] : 1.f;
+  for (int i = threadIdx.x; i < h; i += blockDim.x) {
+    float a = 0.f;
+    for (int k = 0; k < top; ++k) a += to_f32<TA>(y[((int64_t)t * top + k) * h + i]);
+    if (shared) a += g * to_f32<TA>(shared[(int64_t)t * h + i]);
+    out[(int64_t)t * h + i] = from_f32<TA>(a);
+  }
+}
+
+template <typename TA>
+__global__ void activation_kernel(const TA* __restrict__ x, TA* __restrict__ out, int64_t n, int act) {
+  pdl_enter();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    out[i] = from_f32<TA>(activate(to_f32<TA>(x[i]), act));
+}
+
+}  // namespace
+
+DINFER_DEFINE_LAST_ERROR()
+
+// h [T, K] rows of stride ldh; wr [E, K], wg [K] or null (w_dtype); ids, weights [T, top]; gate [T] or null.
+DINFER_API int dinfer_moe_router(const void* h, int64_t ldh, const void* wr, const void* wg, int* ids, float* weights,
+                                 float* gate, int T, int K, int E, int top, int sigmoid_scores, int renorm,
+                                 int act_dtype, int w_dtype, cudaStream_t stream) {
+  if (T < 0 || K <= 0 || E <= 0 || top <= 0 || top > E || ldh < K)
+    return refuse(DINFER_BAD_ARGUMENT, "moe_router: bad sizes T=%d K=%d E=%d top=%d", T, K, E, top);
+  if ((size_t)RW * E * sizeof(float) > 48 * 1024) return refuse(DINFER_BAD_ARGUMENT, "moe_router: %d experts above the limit %d", E, 48 * 1024 / 4 / RW);
+  if (T == 0) return 0;
+  DINFER_DISPATCH_DTYPE(act_dtype, TA,
+    DINFER_DISPATCH_DTYPE(w_dtype, TW, {
+      launch_pdl(moe_router_kernel<TA, TW>, dim3((T + RW - 1) / RW), dim3(RW * 32), (size_t)RW * E * sizeof(float),
+                 stream, (const TA*)h, ldh, (const TW*)wr, (const TW*)wg, ids, weights, gate, T, K, E, top,
+                 sigmoid_scores, renorm);
+      return cuda_status("moe_router");
+    }));
+  return 0;
+}
+
+// ids [pairs]; sorted [cap], cap >= pairs + E * (BM - 1) rounded up to BM; tile_expert [cap / BM].
+DINFER_API int dinfer_moe_align(const int* ids, int* sorted, int* tile_expert, int pairs, int E, int BM, int cap,
+                                cudaStream_t stream) {
+  if (pairs < 0 || E <= 0 || BM <= 0 || cap % BM || cap < pairs + E * (BM - 1))
+    return refuse(DINFER_BAD_ARGUMENT, "moe_align: bad sizes pairs=%d E=%d BM=%d cap=%d", pairs, E, BM, cap);
+  const size_t smem = (size_t)(3 * E + 1) * sizeof(int);
+  if (smem > 48 * 1024) return refuse(DINFER_BAD_ARGUMENT, "moe_align: %d experts above the limit", E);
+  launch_pdl(moe_align_kernel, dim3(1), dim3(1024), smem, stream, ids, sorted, tile_expert, pairs, E, BM, cap, cap / BM);
+  return cuda_status("moe_align");
+}
+
+// mode 0: A = h [T, K] (row of pair p: p / top), C [cap, N] by position, epilogue activation `act`.
+// mode 1: A [cap, K] by position, C [pairs, N] by pair, each row times weights[pair].  W [E, N, K] contiguous.
+DINFER_API int dinfer_moe_gemm(const void* A, int64_t lda, const void* W, void* C, int64_t ldc, const int* sorted,
+                               const int* tile_expert, const float* weights, int pairs, int top, int N, int K, int BM,
+                               int cap, int mode, int act, int act_dtype, int w_dtype, cudaStream_t stream) {
+  if (pairs < 0 || top <= 0 || N <= 0 || K <= 0 || (BM != 16 && BM != 64) || cap % BM || lda < K || ldc < N ||
+      (mode != 0 && mode != 1) || (mode == 1 && !weights))
+    return refuse(DINFER_BAD_ARGUMENT, "moe_gemm: bad arguments pairs=%d N=%d K=%d BM=%d cap=%d mode=%d", pairs, N, K, BM, cap, mode);
+  if (pairs == 0) return 0;
+  dim3 grid((N + 63) / 64, cap / BM);
+  if (grid.y > 65535) return refuse(DINFER_BAD_ARGUMENT, "moe_gemm: too many row tiles (%d)", (int)grid.y);
+#define GO(BM_, MODE_)                                                                                              \
+  launch_pdl(moe_gemm_simt_kernel<TA, TW, BM_, MODE_>, grid, dim3(256), 0, stream, (const TA*)A, lda, (const TW*)W, \
+             (TA*)C, ldc, sorted, tile_expert, weights, pairs, top, N, K, act)
+  DINFER_DISPATCH_DTYPE(act_dtype, TA,
+    DINFER_DISPATCH_DTYPE(w_dtype, TW, {
+      if (BM == 16) { if (mode == 0) GO(16, 0); else GO(16, 1); }
+      else { if (mode == 0) GO(64, 0); else GO(64, 1); }
+      return cuda_status("moe_gemm");
+    }));
+#undef GO
+  return 0;
+}
+
+// y [T * top, h] by pair; shared [T, h] or null with gate [T] or null (1); out [T, h].
+DINFER_API int dinfer_moe_combine(const void* y, const void* shared, const float* gate, void* out, int T, int top,
+                                  int h, int act_dtype, cudaStream_t stream) {
+  if (T < 0 || top <= 0 || h <= 0) return refuse(DINFER_BAD_ARGUMENT, "moe_combine: bad sizes T=%d top=%d h=%d", T, top, h);
+  if (T == 0) return 0;
+  DINFER_DISPATCH_DTYPE(act_dtype, TA, {
+    launch_pdl(moe_combine_kernel<TA>, dim3(T), dim3(256), 0, stream, (const TA*)y, (const TA*)shared, gate, (TA*)out,
+               top, h);
+    return cuda_status("moe_combine");
+  });
+  return 0;
+}
+
+// out = act(x), element by element (1 relu^2, 2 silu, 3 tanh-gelu, 4 relu); out may be x.
+DINFER_API int dinfer_activation(const void* x, void* out, int64_t n, int act, int act_dtype, cudaStream_t stream) {
+  if (n < 0) return refuse(DINFER_BAD_ARGUMENT, "activation: bad size");
+  if (n == 0) return 0;
+  const int blocks = (int)((n + 255) / 256 < 8192 ? (n + 255) / 256 : 8192);
+  DINFER_DISPATCH_DTYPE(act_dtype, TA, {
+    launch_pdl(activation_kernel<TA>, dim3(blocks), dim3(256), 0, stream, (const TA*)x, (TA*)out, n, act);
+    return cuda_status("activation");
+  });
+  return 0;
+}

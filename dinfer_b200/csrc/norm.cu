@@ -136,6 +136,73 @@ __global__ void rmsnorm_plain_kernel(const TA* __restrict__ x, const TW* __restr
     out[(int64_t)blockIdx.x * h + i] = from_f32<TA>(to_f32<TA>(row[i]) * rinv * to_f32<TW>(weight[i]));
 }
 
+
+// Layer norm (weight and bias) over rows of the 32-bit residual stream, with up to two pending branch outputs
+// added first, each times a per-channel scale, and up to two normed outputs of the same row (two norms with their
+// own weights: the layers whose mixer and feed-forward read the same x):
+//
+//   v      = residual[src] + d1[src] * s1 + d2[src] * s2      (each optional; s null = 1; src = rows[r] or r)
+//   residual[src] = v                                         (when a delta is given and rows is not)
+//   mu = mean(v), var = mean((v - mu)^2)                      (two passes over the row kept in shared memory)
+//   out_k[r] = T( (v - mu) * rsqrt(var + eps) * w_k + b_k )   (k = 1, 2; b null = 0)
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(1024)
+layernorm_kernel(float* __restrict__ residual, const TA* __restrict__ d1, const TW* __restrict__ s1,
+                 const TA* __restrict__ d2, const TW* __restrict__ s2, const int* __restrict__ rows,
+                 const TW* __restrict__ w1, const TW* __restrict__ b1, TA* __restrict__ out1,
+                 const TW* __restrict__ w2, const TW* __restrict__ b2, TA* __restrict__ out2, int h, float eps,
+                 int stash) {
+  extern __shared__ float sm_row[];
+  __shared__ float red[33];
+  pdl_enter();
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  float* res = residual + (int64_t)src * h;
+  const TA* e1 = d1 ? d1 + (int64_t)src * h : nullptr;
+  const TA* e2 = d2 ? d2 + (int64_t)src * h : nullptr;
+  const bool writeback = (e1 || e2) && rows == nullptr;
+  auto value = [&](int i) {
+    float v = res[i];
+    if (e1) v += to_f32<TA>(e1[i]) * (s1 ? to_f32<TW>(s1[i]) : 1.f);
+    if (e2) v += to_f32<TA>(e2[i]) * (s2 ? to_f32<TW>(s2[i]) : 1.f);
+    return v;
+  };
+  float sum = 0.f;
+  for (int i = threadIdx.x; i < h; i += blockDim.x) {
+    const float v = value(i);
+    if (stash) sm_row[i] = v;
+    sum += v;
+  }
+  const float mu = block_sum(sum, red) / (float)h;
+  float sq = 0.f;
+  for (int i = threadIdx.x; i < h; i += blockDim.x) {
+    const float d = (stash ? sm_row[i] : value(i)) - mu;
+    sq += d * d;
+  }
+  const float rinv = rsqrtf(block_sum(sq, red) / (float)h + eps);
+  for (int i = threadIdx.x; i < h; i += blockDim.x) {
+    const float v = stash ? sm_row[i] : value(i);
+    const float n = (v - mu) * rinv;
+    out1[(int64_t)r * h + i] = from_f32<TA>(n * to_f32<TW>(w1[i]) + (b1 ? to_f32<TW>(b1[i]) : 0.f));
+    if (out2) out2[(int64_t)r * h + i] = from_f32<TA>(n * to_f32<TW>(w2[i]) + (b2 ? to_f32<TW>(b2[i]) : 0.f));
+    if (writeback) res[i] = v;           // after every read of the old value by this thread (same i, same thread)
+  }
+}
+
+// residual += d1 * s1 + d2 * s2 for rows nobody norms (a pending sum resolved on its own)
+template <typename TA, typename TW>
+__global__ void scaled_add_kernel(float* __restrict__ residual, const TA* __restrict__ d1, const TW* __restrict__ s1,
+                                  const TA* __restrict__ d2, const TW* __restrict__ s2, int64_t n, int h) {
+  pdl_enter();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % h);
+    float v = residual[i];
+    if (d1) v += to_f32<TA>(d1[i]) * (s1 ? to_f32<TW>(s1[c]) : 1.f);
+    if (d2) v += to_f32<TA>(d2[i]) * (s2 ? to_f32<TW>(s2[c]) : 1.f);
+    residual[i] = v;
+  }
+}
+
 }  // namespace
 
 DINFER_DEFINE_LAST_ERROR()
@@ -162,6 +229,45 @@ DINFER_API int dinfer_rmsnorm_plain(const void* x, const void* weight, void* out
     DINFER_DISPATCH_DTYPE(w_dtype, TW, {
       rmsnorm_plain_kernel<TA, TW><<<num_rows, threads, 0, stream>>>((const TA*)x, (const TW*)weight, (TA*)out, h, eps);
       return cuda_status("rmsnorm_plain");
+    }));
+  return 0;
+}
+
+// residual [*, h] f32 (updated in place when a delta is given and rows is null); d1, d2 [*, h] act dtype or null with
+// their per-channel scales s1, s2 [h] (null: 1); rows [num_rows] int32 or null; w1, b1 (and w2, b2 with out2) [h];
+// out1, out2 [num_rows, h] act dtype (out2 null: one norm).
+DINFER_API int dinfer_layernorm(float* residual, const void* d1, const void* s1, const void* d2, const void* s2,
+                                const int* rows, const void* w1, const void* b1, void* out1, const void* w2,
+                                const void* b2, void* out2, int num_rows, int h, float eps, int act_dtype,
+                                int w_dtype, cudaStream_t stream) {
+  if (h <= 0 || num_rows < 0) return refuse(DINFER_BAD_ARGUMENT, "layernorm: bad sizes rows=%d h=%d", num_rows, h);
+  if (!w1 || !out1 || (out2 && !w2)) return refuse(DINFER_BAD_ARGUMENT, "layernorm: an output without its weight");
+  if (num_rows == 0) return 0;
+  int threads = (h + 31) / 32 * 32;
+  if (threads > 1024) threads = 1024;
+  const size_t row_bytes = (size_t)h * sizeof(float);
+  const int stash = row_bytes <= 48 * 1024;
+  DINFER_DISPATCH_DTYPE(act_dtype, TA,
+    DINFER_DISPATCH_DTYPE(w_dtype, TW, {
+      launch_pdl(layernorm_kernel<TA, TW>, dim3(num_rows), dim3(threads), stash ? row_bytes : 0, stream, residual,
+                 (const TA*)d1, (const TW*)s1, (const TA*)d2, (const TW*)s2, rows, (const TW*)w1, (const TW*)b1,
+                 (TA*)out1, (const TW*)w2, (const TW*)b2, (TA*)out2, h, eps, stash);
+      return cuda_status("layernorm");
+    }));
+  return 0;
+}
+
+DINFER_API int dinfer_scaled_add(float* residual, const void* d1, const void* s1, const void* d2, const void* s2,
+                                 int num_rows, int h, int act_dtype, int w_dtype, cudaStream_t stream) {
+  if (h <= 0 || num_rows < 0) return refuse(DINFER_BAD_ARGUMENT, "scaled_add: bad sizes rows=%d h=%d", num_rows, h);
+  if (num_rows == 0 || (!d1 && !d2)) return 0;
+  const int64_t n = (int64_t)num_rows * h;
+  const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+  DINFER_DISPATCH_DTYPE(act_dtype, TA,
+    DINFER_DISPATCH_DTYPE(w_dtype, TW, {
+      launch_pdl(scaled_add_kernel<TA, TW>, dim3(blocks), dim3(256), 0, stream, residual, (const TA*)d1,
+                 (const TW*)s1, (const TA*)d2, (const TW*)s2, n, h);
+      return cuda_status("scaled_add");
     }));
   return 0;
 }

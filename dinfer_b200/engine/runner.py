@@ -117,7 +117,9 @@ class ModelRunner:
         if engine.max_model_len > self.spec.max_positions:
             raise ValueError(f"max_model_len {engine.max_model_len} exceeds the model's "
                              f"max_position_embeddings {self.spec.max_positions}")
-        env = BuildEnv(self.device, self.act_dtype, self.spec.hidden_size, self.spec.max_positions)
+        # position tables are made for the longest request this engine takes, not for the longest the model could
+        env = BuildEnv(self.device, self.act_dtype, self.spec.hidden_size,
+                       min(self.spec.max_positions, engine.max_model_len))
         self.model = DecoderModel(self.spec, env)
         # where the start-up time goes, in seconds (the reference logs such phases: crates/layers/src/load.rs:35-136)
         t0 = time.perf_counter()
@@ -140,7 +142,8 @@ class ModelRunner:
         self.plan = PlanBuilder(self.manager, self.device,
                                 max_tokens=engine.max_num_batched_tokens + engine.max_num_seqs,
                                 max_reqs=engine.max_num_seqs + self.PROMPT_PLACES[-1],
-                                max_blocks=self.max_blocks_per_seq, max_positions=self.spec.max_positions,
+                                max_blocks=self.max_blocks_per_seq,
+                                max_positions=min(self.spec.max_positions, engine.max_model_len),
                                 spare_state_slot=engine.max_num_seqs)
         # the tokens the last step sampled stay here (a fixed address, so that captured graphs can read it):
         # a step launched before the host has read them names them by row (see StepEntry.tokens)
@@ -181,7 +184,7 @@ class ModelRunner:
         # one table width for all groups: what the group with the smallest pages needs
         self.max_blocks_per_seq = max([(e.max_model_len + b - 1) // b for b in sizes] or [(e.max_model_len + bs - 1) // bs])
         elt = 4 if self.act_dtype == torch.float32 else 2
-        bytes_per_token = sum(2 * n.num_kv_heads * n.head_dim * elt for n in needs if isinstance(n, KvCacheNeed))
+        bytes_per_token = sum(n.planes * n.num_kv_heads * n.head_dim * elt for n in needs if isinstance(n, KvCacheNeed))
         # every group gets pages for the same number of tokens: ``num_blocks`` pages of the engine's page size
         longest = (e.max_model_len + bs - 1) // bs
         if e.num_blocks is not None:
@@ -214,7 +217,7 @@ class ModelRunner:
                 self.bindings.append(CacheBinding(kv=src.kv, group=src.group, write=False, state=src.state))
             elif isinstance(n, KvCacheNeed):
                 g = entry_group[i]
-                kv = torch.zeros((group_blocks[g], 2, n.num_kv_heads, sizes[g], n.head_dim),
+                kv = torch.zeros((group_blocks[g], n.planes, n.num_kv_heads, sizes[g], n.head_dim),
                                  dtype=self.act_dtype, device=self.device)
                 self.bindings.append(CacheBinding(kv=kv, group=entry_group[i], write=True))
             elif isinstance(n, StateNeed):

@@ -1,0 +1,111 @@
+"""Wrappers of the routed feed-forward's kernels (``csrc/moe.cu``)."""
+from __future__ import annotations
+
+from ctypes import c_float, c_int, c_int64, c_void_p
+from typing import Optional, Tuple
+
+import torch
+
+from .lib import KernelError, check, dtype_code, ptr, require_cuda, stream_handle
+from .ops import _fn, _rows_contiguous
+
+ACTIVATIONS = {"none": 0, "relu2": 1, "silu": 2, "gelu_tanh": 3, "relu": 4}
+
+
+def router(h: torch.Tensor, w_router: torch.Tensor, top_k: int, scoring: str = "softmax", renormalize: bool = False,
+           w_gate: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
+    """32-bit router: (expert ids int32 [T, top_k], weights f32 [T, top_k], gate f32 [T] or None).  ``scoring``
+    softmax (over all experts) or sigmoid; the weights are the chosen scores, divided by their sum with
+    ``renormalize``; ``w_gate`` [1, K]: gate[t] = sigmoid(w_gate . h[t])."""
+    require_cuda(h, w_router, w_gate)
+    _rows_contiguous(h, "moe router")
+    T, K = h.shape
+    E = w_router.shape[0]
+    if scoring not in ("softmax", "sigmoid"):
+        raise KernelError(f"moe router: unknown scoring {scoring!r}")
+    if w_router.shape[1] != K or not w_router.is_contiguous():
+        raise KernelError("moe router: weight [E, K] contiguous")
+    if w_gate is not None and (w_gate.numel() != K or w_gate.dtype != w_router.dtype or not w_gate.is_contiguous()):
+        raise KernelError("moe router: gate weight [K] of the router's dtype")
+    ids = torch.empty((T, top_k), dtype=torch.int32, device=h.device)
+    weights = torch.empty((T, top_k), dtype=torch.float32, device=h.device)
+    gate = torch.empty((T,), dtype=torch.float32, device=h.device) if w_gate is not None else None
+    lib, f = _fn("moe", "dinfer_moe_router",
+                 [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                  c_int, c_int, c_int, c_void_p])
+    check(lib, f(ptr(h), h.stride(0), ptr(w_router), ptr(w_gate), ptr(ids), ptr(weights), ptr(gate), T, K, E, top_k,
+                 int(scoring == "sigmoid"), int(bool(renormalize)), dtype_code(h.dtype), dtype_code(w_router.dtype),
+                 stream_handle()), "moe_router")
+    return ids, weights, gate
+
+
+def row_tile(pairs: int, num_experts: int) -> int:
+    """Rows of a tile of the grouped products: 16 while an expert gets few rows (decode steps), else 64."""
+    return 16 if pairs <= 16 * num_experts else 64
+
+
+def align(ids: torch.Tensor, num_experts: int, tile: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The (token, choice) pairs laid out expert by expert, each expert's run padded to a multiple of ``tile``:
+    (sorted int32 [cap]: pair index or ``pairs`` for padding; tile_expert int32 [cap / tile]: expert or -1)."""
+    require_cuda(ids)
+    if ids.dtype != torch.int32 or not ids.is_contiguous():
+        raise KernelError("moe align: ids int32 contiguous")
+    pairs = ids.numel()
+    cap = (pairs + num_experts * (tile - 1) + tile - 1) // tile * tile
+    sorted_ = torch.empty((cap,), dtype=torch.int32, device=ids.device)
+    tile_expert = torch.empty((cap // tile,), dtype=torch.int32, device=ids.device)
+    lib, f = _fn("moe", "dinfer_moe_align", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    check(lib, f(ptr(ids), ptr(sorted_), ptr(tile_expert), pairs, num_experts, tile, cap, stream_handle()), "moe_align")
+    return sorted_, tile_expert
+
+
+def grouped_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, sorted_: torch.Tensor, tile_expert: torch.Tensor,
+                 pairs: int, top_k: int, tile: int, mode: int, activation: str = "none",
+                 weights: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """mode 0: ``out[pos] = act(a[pair // top_k] @ w[e]^T)`` for every position of the layout (a [T, K], out [cap, N]);
+    mode 1: ``out[pair] = (a[pos] @ w[e]^T) * weights[pair]`` (a [cap, K], out [pairs, N]).  w [E, N, K]."""
+    require_cuda(a, w, out, sorted_, tile_expert, weights)
+    _rows_contiguous(a, "moe gemm a")
+    _rows_contiguous(out, "moe gemm out")
+    E, N, K = w.shape
+    cap = sorted_.numel()
+    if not w.is_contiguous() or a.shape[1] != K or out.shape[1] != N or out.dtype != a.dtype:
+        raise KernelError("moe gemm: w [E, N, K] contiguous, a [*, K], out [*, N] of a's dtype")
+    if (mode == 0 and out.shape[0] != cap) or (mode == 1 and (a.shape[0] != cap or out.shape[0] != pairs)):
+        raise KernelError("moe gemm: row counts do not fit the layout")
+    if mode == 1 and (weights is None or weights.dtype != torch.float32 or weights.numel() != pairs):
+        raise KernelError("moe gemm: mode 1 needs the routing weights, f32 [pairs]")
+    lib, f = _fn("moe", "dinfer_moe_gemm",
+                 [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                  c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    check(lib, f(ptr(a), a.stride(0), ptr(w), ptr(out), out.stride(0), ptr(sorted_), ptr(tile_expert), ptr(weights),
+                 pairs, top_k, N, K, tile, cap, mode, ACTIVATIONS[activation], dtype_code(a.dtype), dtype_code(w.dtype),
+                 stream_handle()), "moe_gemm")
+    return out
+
+
+def combine(y: torch.Tensor, out: torch.Tensor, top_k: int, shared: Optional[torch.Tensor] = None,
+            gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = sum_k y[t * top_k + k] (+ gate[t] * shared[t]), summed in the order of the choices."""
+    require_cuda(y, out, shared, gate)
+    T, h = out.shape
+    if tuple(y.shape) != (T * top_k, h) or not y.is_contiguous() or not out.is_contiguous() or y.dtype != out.dtype:
+        raise KernelError("moe combine: y [T * top_k, h], out [T, h] contiguous of one dtype")
+    if shared is not None and (tuple(shared.shape) != (T, h) or not shared.is_contiguous() or shared.dtype != out.dtype):
+        raise KernelError("moe combine: shared [T, h] contiguous")
+    if gate is not None and (gate.dtype != torch.float32 or gate.numel() != T):
+        raise KernelError("moe combine: gate f32 [T]")
+    lib, f = _fn("moe", "dinfer_moe_combine", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    check(lib, f(ptr(y), ptr(shared), ptr(gate), ptr(out), T, top_k, h, dtype_code(out.dtype), stream_handle()),
+          "moe_combine")
+    return out
+
+
+def activation(x: torch.Tensor, out: torch.Tensor, kind: str) -> torch.Tensor:
+    """out = act(x) element by element (``out`` may be ``x``)."""
+    require_cuda(x, out)
+    if not x.is_contiguous() or not out.is_contiguous() or x.shape != out.shape or x.dtype != out.dtype:
+        raise KernelError("activation: contiguous tensors of one shape and dtype")
+    lib, f = _fn("moe", "dinfer_activation", [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p])
+    check(lib, f(ptr(x), ptr(out), x.numel(), ACTIVATIONS[kind], dtype_code(x.dtype), stream_handle()), "activation")
+    return out

@@ -222,3 +222,115 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, b
                  head_dim, cache.shape[3], float(scale), int(window), dtype_code(q.dtype), stream_handle()),
           "attention_generic")
     return out
+
+
+def _opt_vec(t: Optional[torch.Tensor], h: int, dt: torch.dtype, what: str) -> None:
+    if t is not None and (t.numel() != h or t.dtype != dt or not t.is_contiguous()):
+        raise KernelError(f"{what} must be [{h}] of {dt}, contiguous")
+
+
+def layernorm(residual: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float, out: torch.Tensor,
+              deltas=(), rows: Optional[torch.Tensor] = None, weight2: Optional[torch.Tensor] = None,
+              bias2: Optional[torch.Tensor] = None, out2: Optional[torch.Tensor] = None):
+    """Layer norm of ``v = residual[src] + sum_i deltas[i][0][src] * deltas[i][1]`` (up to two deltas, each with a
+    per-channel scale or None; src = rows[r] or r) with weight and bias; with ``out2`` a second norm of the same
+    rows with its own weight and bias.  The sum is written back to ``residual`` when a delta is given and
+    ``rows`` is not."""
+    deltas = [d for d in deltas if d is not None]
+    if len(deltas) > 2:
+        raise KernelError("layernorm: at most two pending deltas")
+    require_cuda(residual, weight, bias, out, rows, weight2, bias2, out2)
+    h = residual.shape[-1]
+    if residual.dtype != torch.float32 or not residual.is_contiguous():
+        raise KernelError("layernorm: residual must be contiguous float32")
+    wdt = weight.dtype
+    for t, n in ((weight, "weight"), (bias, "bias"), (weight2, "weight2"), (bias2, "bias2")):
+        _opt_vec(t, h, wdt, "layernorm: " + n)
+    n = rows.numel() if rows is not None else residual.shape[0]
+    if rows is not None and rows.dtype != torch.int32:
+        raise KernelError("layernorm: rows must be int32")
+    for o in (out, out2):
+        if o is not None and (not o.is_contiguous() or tuple(o.shape) != (n, h) or o.dtype != out.dtype):
+            raise KernelError("layernorm: outputs [R, h] contiguous of one dtype")
+    if out2 is not None and weight2 is None:
+        raise KernelError("layernorm: a second output needs its weight")
+    args = []
+    for d, s in deltas + [(None, None)] * (2 - len(deltas)):
+        if d is not None:
+            require_cuda(d, s)
+            if d.dtype != out.dtype or d.shape != residual.shape or not d.is_contiguous():
+                raise KernelError("layernorm: a delta must have the residual's shape and the output's dtype")
+            _opt_vec(s, h, wdt, "layernorm: a delta's scale")
+        args += [ptr(d), ptr(s)]
+    lib, f = _fn("norm", "dinfer_layernorm", [c_void_p] * 12 + [c_int, c_int, c_float, c_int, c_int, c_void_p])
+    check(lib, f(ptr(residual), *args, ptr(rows), ptr(weight), ptr(bias), ptr(out), ptr(weight2), ptr(bias2), ptr(out2),
+                 n, h, float(eps), dtype_code(out.dtype), dtype_code(wdt), stream_handle()), "layernorm")
+    return out if out2 is None else (out, out2)
+
+
+def scaled_add(residual: torch.Tensor, deltas) -> torch.Tensor:
+    """residual += sum_i deltas[i][0] * deltas[i][1] (up to two; a scale [h] or None), 32-bit, in place."""
+    deltas = [d for d in deltas if d is not None and d[0] is not None]
+    if not deltas:
+        return residual
+    if len(deltas) > 2:
+        raise KernelError("scaled_add: at most two deltas")
+    h = residual.shape[-1]
+    if residual.dtype != torch.float32 or not residual.is_contiguous():
+        raise KernelError("scaled_add: residual must be contiguous float32")
+    adt = deltas[0][0].dtype
+    wdt = next((s.dtype for _, s in deltas if s is not None), torch.float32)
+    args = []
+    for d, s in deltas + [(None, None)] * (2 - len(deltas)):
+        if d is not None:
+            require_cuda(d, s)
+            if d.dtype != adt or d.shape != residual.shape or not d.is_contiguous():
+                raise KernelError("scaled_add: a delta must have the residual's shape")
+            _opt_vec(s, h, wdt, "scaled_add: a scale")
+        args += [ptr(d), ptr(s)]
+    lib, f = _fn("norm", "dinfer_scaled_add", [c_void_p] * 5 + [c_int, c_int, c_int, c_int, c_void_p])
+    check(lib, f(ptr(residual), *args, residual.numel() // h, h, dtype_code(adt), dtype_code(wdt), stream_handle()),
+          "scaled_add")
+    return residual
+
+
+GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "relu": 2, "relu2": 3}
+
+
+def gated_act(x: torch.Tensor, out: torch.Tensor, activation: str = "silu", pairs: bool = False) -> torch.Tensor:
+    """out[t, i] = act(gate_i) * up_i; the layouts of ``silu_mul``; ``activation`` a key of ``GATE_ACTIVATIONS``."""
+    if activation == "silu":
+        return silu_mul(x, out, pairs)
+    require_cuda(x, out)
+    _rows_contiguous(x, "gated_act")
+    T, two_i = x.shape
+    inter = two_i // 2
+    if activation not in GATE_ACTIVATIONS:
+        raise KernelError(f"gated_act: unknown activation {activation!r}")
+    if two_i % 2 or out.shape != (T, inter) or not out.is_contiguous() or out.dtype != x.dtype:
+        raise KernelError("gated_act: x [T, 2I], out [T, I] contiguous, same dtype")
+    lib, f = _fn("elementwise", "dinfer_gated_act", [c_void_p, c_void_p, c_int, c_int, c_int64, c_int, c_int, c_int, c_void_p])
+    check(lib, f(ptr(x), ptr(out), T, inter, x.stride(0), dtype_code(x.dtype), int(bool(pairs)),
+                 GATE_ACTIVATIONS[activation], stream_handle()), "gated_act")
+    return out
+
+
+def gemm_f32_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[:, b, :] = a[:, b, :] @ w[b]^T for every b: a [M, B, K], w [B, N, K], out [M, B, N] (any views whose last
+    axis is contiguous, e.g. the heads of a row); 32-bit multiply-adds on the CUDA cores, operands f32 or bf16."""
+    require_cuda(a, w, out)
+    if a.dim() != 3 or w.dim() != 3 or out.dim() != 3:
+        raise KernelError("gemm_f32_batched: a [M, B, K], w [B, N, K], out [M, B, N]")
+    M, B, K = a.shape
+    N = w.shape[1]
+    if w.shape[0] != B or w.shape[2] != K or tuple(out.shape) != (M, B, N):
+        raise KernelError(f"gemm_f32_batched: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not agree")
+    for t in (a, w, out):
+        _rows_contiguous(t, "gemm_f32_batched")
+    lib, f = _fn("gemm_f32", "dinfer_gemm_f32_batched",
+                 [c_void_p, c_int64, c_int64, c_int, c_void_p, c_int64, c_int64, c_int, c_void_p, c_int64, c_int64, c_int,
+                  c_int, c_int, c_int, c_int, c_void_p])
+    check(lib, f(ptr(a), a.stride(0), a.stride(1), dtype_code(a.dtype), ptr(w), w.stride(1), w.stride(0),
+                 dtype_code(w.dtype), ptr(out), out.stride(0), out.stride(1), dtype_code(out.dtype), M, N, K, B,
+                 stream_handle()), "gemm_f32_batched")
+    return out

@@ -11,7 +11,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..kernels import ops
-from ..parts import attention, block, mlp, norm, rope  # noqa: F401  (register the built-in parts)
+from ..parts import attention, block, latent_attention, mlp, moe, norm, rope  # noqa: F401  (register the built-in parts)
 from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, BuildEnv, CacheBinding, ResidualStream,
                           StepContext, build_part)
 from ..parts.linear import Linear
@@ -30,7 +30,9 @@ class DecoderModel:
             mnorm = build_part(NORMS, ls.mixer_norm, env, ls.prefix)
             ffn = build_part(FEED_FORWARDS, ls.feed_forward, env, ls.prefix)
             fnorm = build_part(NORMS, ls.feed_forward_norm, env, ls.prefix)
-            self.blocks.append(BLOCKS.get(ls.block)(mixer, mnorm, ffn, fnorm))
+            blk = BLOCKS.get(ls.block)(mixer, mnorm, ffn, fnorm)
+            blk.configure(ls.extras, env, ls.prefix)
+            self.blocks.append(blk)
         self.final_norm = build_part(NORMS, spec.final_norm, env, "")
         self.embedding: Optional[torch.Tensor] = None
         self.lm_head: Optional[Linear] = None
@@ -42,6 +44,7 @@ class DecoderModel:
         for b in self.blocks:
             for p in b.parts():
                 d += p.declare()
+            d += b.declare()
         d += self.final_norm.declare()
         # the head falls back to the embedding table only when the configuration ties them
         # (models/qwen3/src/model.rs:487-496)
@@ -54,6 +57,7 @@ class DecoderModel:
         for b in self.blocks:
             for p in b.parts():
                 p.bind(tensors)
+            b.bind(tensors)
         self.final_norm.bind(tensors)
         head = tensors.get(s.lm_head_tensor)
         self.lm_head = Linear(head if head is not None else self.embedding)
@@ -63,6 +67,7 @@ class DecoderModel:
         for b in self.blocks:
             for p in b.parts():
                 libs += p.kernel_libraries()
+            libs += b.kernel_libraries()
         return list(dict.fromkeys(libs))
 
     # ---- caches

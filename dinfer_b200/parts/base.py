@@ -25,11 +25,14 @@ from .spec import PartSpec, TensorDecl
 @dataclass(frozen=True)
 class KvCacheNeed:
     """Keys and values of every token (``window`` None) or of the last ``window`` tokens, in pages of
-    ``block_size`` tokens (None: the engine's page size)."""
+    ``block_size`` tokens (None: the engine's page size).  ``planes``: 2 = keys and values apart
+    (``[pages, 2, Hkv, page, D]``); 1 = one row per token that serves as both (a latent cache:
+    ``[pages, 1, Hkv, page, D]``)."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     block_size: Optional[int] = None
+    planes: int = 2
 
     def group_key(self):
         # layers whose pages live and die together: same span of tokens, same page size
@@ -186,6 +189,22 @@ class PositionEncoding(Part):
 
 
 @dataclass
+class ScaledDeltas:
+    """Branch outputs that are not in the residual yet: ``residual += sum_i tensor_i * scale_i`` (a per-channel
+    scale [h] or None for 1).  At most two.  A norm that understands them adds them in its own kernel; any other
+    consumer resolves them first (``resolve_pending``)."""
+    items: List[Tuple[torch.Tensor, Optional[torch.Tensor]]]
+
+
+def resolve_pending(stream: "ResidualStream") -> None:
+    """Add a pending ``ScaledDeltas`` into the residual now (for consumers that only take a plain delta)."""
+    if isinstance(stream.pending, ScaledDeltas):
+        from ..kernels import ops
+        ops.scaled_add(stream.x, stream.pending.items)
+        stream.pending = None
+
+
+@dataclass
 class ResidualStream:
     """The 32-bit residual ``x`` and either a part's output that has not been added to it yet (``pending``) or
     the input of the next block's mixer, already added and half normed by the part before (``half``, made for
@@ -201,8 +220,22 @@ class Block:
         self.mixer, self.mixer_norm = mixer, mixer_norm
         self.feed_forward, self.feed_forward_norm = feed_forward, feed_forward_norm
 
+    def configure(self, extras: Mapping[str, Any], env: "BuildEnv", prefix: str) -> None:
+        """What the arrangement itself takes (``LayerSpec.extras``); called once, before ``declare``."""
+        self.extras, self.env, self.prefix = dict(extras or {}), env, prefix
+
     def parts(self) -> List[Part]:
         return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+
+    def declare(self) -> List[TensorDecl]:
+        """Tensors of the arrangement itself (the parts declare their own)."""
+        return []
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        pass
+
+    def kernel_libraries(self) -> List[str]:
+        return []
 
     def forward(self, stream: ResidualStream, ctx: StepContext, cache: CacheBinding,
                 next_block: Optional["Block"] = None) -> None:

@@ -52,3 +52,64 @@ class PreNormResidual(Block):
             stream.half_norm = next_block.mixer_norm
         else:
             stream.pending = self.feed_forward.forward(h, ctx)
+
+
+@BLOCKS.register("parallel_residual")
+class ParallelResidual(Block):
+    """``x += s1 * mixer(norm1(x)) + s2 * ffn(norm2(x))``: both branches read the same ``x``.
+
+    extras: ``mixer_scale`` / ``feed_forward_scale``: tensor names (after the layer's prefix) of per-channel
+    scales [h] of the two branches (layer scale); absent = 1.  A layer may have no feed-forward (kind "none").
+
+    Neither branch output is added by a kernel of its own: both stay pending (``ScaledDeltas``) until the next
+    layer's (or the model's final) norm, whose kernel computes ``x + s1 * a + s2 * f`` in 32-bit, writes it back and
+    norms it.  When the two norms are layer norms of one size they run as one kernel (one mean and variance, two
+    weights and biases)."""
+
+    def declare(self):
+        from .spec import TensorDecl
+        h = self.env.hidden_size
+        d = []
+        if self.extras.get("mixer_scale"):
+            d.append(TensorDecl(self.prefix + self.extras["mixer_scale"], (h,), init="ones"))
+        if self.extras.get("feed_forward_scale"):
+            d.append(TensorDecl(self.prefix + self.extras["feed_forward_scale"], (h,), init="ones",
+                                optional=self._no_feed_forward()))
+        return d
+
+    def _no_feed_forward(self) -> bool:
+        return bool(getattr(self.feed_forward, "absent", False))
+
+    def bind(self, tensors):
+        def get(key):
+            name = self.extras.get(key)
+            t = tensors.get(self.prefix + name) if name else None
+            return None if t is None else t.contiguous()
+        self.mixer_scale, self.feed_forward_scale = get("mixer_scale"), get("feed_forward_scale")
+        scales = [s for s in (self.mixer_scale, self.feed_forward_scale) if s is not None]
+        if len(scales) == 2 and scales[0].dtype != scales[1].dtype:
+            self.mixer_scale, self.feed_forward_scale = (s.float() for s in scales)
+
+    def kernel_libraries(self):
+        return ["norm"]
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, cache: CacheBinding,
+                next_block: Optional[Block] = None) -> None:
+        from .base import ScaledDeltas, resolve_pending
+        from .norm import LayerNorm
+        if stream.half is not None:
+            raise RuntimeError("a parallel block does not take half-normed rows")
+        n1, n2 = self.mixer_norm, self.feed_forward_norm
+        if self._no_feed_forward():
+            h1, h2 = n1.forward(stream.x, delta=stream.pending), None
+        elif isinstance(n1, LayerNorm) and isinstance(n2, LayerNorm) and n1.size == n2.size and n1.eps == n2.eps:
+            h1, h2 = n1.forward_pair(n2, stream.x, delta=stream.pending)
+        else:
+            h1 = n1.forward(stream.x, delta=stream.pending)
+            h2 = n2.forward(stream.x)
+        stream.pending = None
+        a = self.mixer.forward(h1, ctx, cache)
+        items = [(a, self.mixer_scale)]
+        if h2 is not None:
+            items.append((self.feed_forward.forward(h2, ctx), self.feed_forward_scale))
+        stream.pending = ScaledDeltas(items)

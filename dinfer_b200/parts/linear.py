@@ -63,9 +63,12 @@ class Linear:
         return (self.bias is None and act_dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < rows <= TC_MAX_DECODE_TOKENS
                 and self.in_features % 8 == 0 and self.out_features % 8 == 0 and w.data_ptr() % 16 == 0)
 
-    def gated_pairs(self, x) -> torch.Tensor:
-        """For a weight whose rows are (gate, up) pairs: ``silu(x gate_j^T) * (x up_j^T)``, [rows, out/2].
-        One kernel where ``fuses_gate``, else the product followed by the gate kernel."""
+    def gated_pairs(self, x, activation: str = "silu") -> torch.Tensor:
+        """For a weight whose rows are (gate, up) pairs: ``act(x gate_j^T) * (x up_j^T)``, [rows, out/2].
+        One kernel where ``fuses_gate`` (the silu gate), else the product followed by the gate kernel."""
+        if activation != "silu":
+            act = torch.empty((x.shape[0], self.out_features // 2), dtype=x.dtype, device=x.device)
+            return ops.gated_act(self(x), act, activation, pairs=True)
         if isinstance(x, HalfNormed):
             act = torch.empty((x.shape[0], self.out_features // 2), dtype=x.xw.dtype, device=x.xw.device)
             return gemm_ops.gemm_tc(x.xw, self.weight, act, gated=True, row_scale=(x.sums, x.parts, x.size, x.eps))

@@ -15,14 +15,29 @@ from .linear import Linear
 from .spec import TensorDecl
 
 
+@FEED_FORWARDS.register("none")
+class NoFeedForward(FeedForward):
+    """A layer without a feed-forward: arrangements that know of it (``absent``) skip the branch."""
+    absent = True
+
+    def forward(self, x, ctx=None, sink=None):
+        raise RuntimeError("this layer has no feed-forward")
+
+
+@FEED_FORWARDS.register("gated_mlp")
 @FEED_FORWARDS.register("swiglu")
 class SwiGLU(FeedForward):
-    """params: ``intermediate_size``, optional tensor names ``gate_proj``, ``up_proj``, ``down_proj``."""
+    """``down( act(gate(x)) * up(x) )``.  params: ``intermediate_size``, optional ``activation`` (silu, the default;
+    gelu_tanh, relu, relu2) and tensor names ``gate_proj``, ``up_proj``, ``down_proj``."""
 
     def __init__(self, params, env, prefix=""):
         super().__init__(params, env, prefix)
         self.hidden = env.hidden_size
         self.inter = int(params["intermediate_size"])
+        self.activation = str(params.get("activation", "silu"))
+        from ..kernels.ops import GATE_ACTIVATIONS
+        if self.activation not in GATE_ACTIVATIONS:
+            raise ValueError(f"gated feed-forward: unknown activation {self.activation!r} ({', '.join(GATE_ACTIVATIONS)})")
         n = lambda key, default: prefix + params.get(key, default)
         self.names = {"g": n("gate_proj", "gate_proj.weight"), "u": n("up_proj", "up_proj.weight"),
                       "d": n("down_proj", "down_proj.weight")}
@@ -45,13 +60,14 @@ class SwiGLU(FeedForward):
         return ["elementwise"] + self.gate_up.kernel_libraries() + self.down.kernel_libraries()
 
     def takes_half_normed(self, rows: int) -> bool:
-        return self.gate_up.fuses_norm(rows, self.env.act_dtype) and self.gate_up.out_features % 2 == 0
+        return (self.activation == "silu" and self.gate_up.fuses_norm(rows, self.env.act_dtype)
+                and self.gate_up.out_features % 2 == 0)
 
     def adds_into_residual(self, rows: int) -> bool:
         return self.down.fuses_norm(rows, self.env.act_dtype)
 
     def forward(self, x, ctx=None, sink=None):
-        act = self.gate_up.gated_pairs(x)
+        act = self.gate_up.gated_pairs(x, self.activation)
         if sink is not None:                               # (residual, the norm behind this feed-forward)
             return self.down.into_residual(act, sink[0], sink[1])
         return self.down(act)

@@ -1,0 +1,106 @@
+"""A routed feed-forward: a 32-bit router picks ``top_k`` of ``num_experts`` small feed-forwards per token, their
+outputs are summed with the router's weights, and an optional shared expert runs for every token.
+
+Data flow of one step (nothing goes through the host; every size is fixed by the number of tokens, so the step
+can be captured in a CUDA graph):
+  ids, w, g = router(x)                 f32 logits -> scores -> top-k (+ the shared expert's gate)
+  layout    = align(ids)                (token, choice) pairs expert by expert, runs padded to the row tile
+  u         = act(x[pair] W_up[e]^T)    grouped product, rows gathered
+  y[pair]   = (u W_down[e]^T) * w[pair] grouped product, rows scattered back
+  out[t]    = sum_k y[t, k] + g[t] * shared(x[t])
+The experts' matrices are stacked at load into ``[E, ff, h]`` and ``[E, h, ff]``.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..kernels import moe_ops
+from .base import FEED_FORWARDS, FeedForward
+from .linear import Linear
+from .spec import TensorDecl
+
+
+@FEED_FORWARDS.register("moe")
+class MoE(FeedForward):
+    """params: ``num_experts``, ``top_k``, ``expert_size``, ``activation`` (relu2, silu, gelu_tanh, relu: experts are
+    ``down(act(up(x)))`` without a gate), ``scoring`` (softmax over all experts, or sigmoid), ``renormalize`` (the
+    chosen scores divided by their sum), ``shared_size`` (0: no shared expert), ``shared_gate`` ("sigmoid": the
+    shared expert's output times ``sigmoid(w_g . x)``; None: added as it is), and the tensor names ``router``,
+    ``expert_up`` / ``expert_down`` (with ``{e}`` for the expert's index), ``shared_up``, ``shared_down``,
+    ``shared_gate_proj``."""
+
+    def __init__(self, params, env, prefix=""):
+        super().__init__(params, env, prefix)
+        p = self.params
+        self.hidden = env.hidden_size
+        self.E, self.top = int(p["num_experts"]), int(p["top_k"])
+        self.ff = int(p["expert_size"])
+        self.shared_ff = int(p.get("shared_size", 0) or 0)
+        self.activation = str(p.get("activation", "relu2"))
+        self.scoring = str(p.get("scoring", "softmax"))
+        self.renormalize = bool(p.get("renormalize", False))
+        self.shared_gate = p.get("shared_gate")
+        if not (0 < self.top <= self.E):
+            raise ValueError(f"moe: top_k {self.top} must be between 1 and num_experts {self.E}")
+        if self.activation not in moe_ops.ACTIVATIONS or self.activation == "none":
+            raise ValueError(f"moe: unknown activation {self.activation!r}")
+        if self.scoring not in ("softmax", "sigmoid") or self.shared_gate not in (None, "sigmoid"):
+            raise ValueError("moe: scoring is softmax or sigmoid, shared_gate sigmoid or None")
+        n = lambda key, default: prefix + p.get(key, default)
+        self.names = {"router": n("router", "router.weight"), "up": n("expert_up", "experts.{e}.up.weight"),
+                      "down": n("expert_down", "experts.{e}.down.weight"), "s_up": n("shared_up", "shared.up.weight"),
+                      "s_down": n("shared_down", "shared.down.weight"), "s_gate": n("shared_gate_proj", "shared.gate.weight")}
+        self.router_w = self.gate_w = self.w_up = self.w_down = None
+        self.shared_up: Optional[Linear] = None
+        self.shared_down: Optional[Linear] = None
+
+    def declare(self) -> List[TensorDecl]:
+        h = self.hidden
+        d = [TensorDecl(self.names["router"], (self.E, h))]
+        for e in range(self.E):
+            d += [TensorDecl(self.names["up"].format(e=e), (self.ff, h)),
+                  TensorDecl(self.names["down"].format(e=e), (h, self.ff))]
+        if self.shared_ff:
+            d += [TensorDecl(self.names["s_up"], (self.shared_ff, h)), TensorDecl(self.names["s_down"], (h, self.shared_ff))]
+            if self.shared_gate:
+                d.append(TensorDecl(self.names["s_gate"], (1, h)))
+        return d
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.router_w = tensors[self.names["router"]].contiguous()
+        ups = [tensors[self.names["up"].format(e=e)] for e in range(self.E)]
+        downs = [tensors[self.names["down"].format(e=e)] for e in range(self.E)]
+        dt = torch.float32 if any(t.dtype == torch.float32 for t in ups + downs) else ups[0].dtype
+        self.w_up = torch.stack([t.to(dt) for t in ups]).contiguous()          # [E, ff, h]
+        self.w_down = torch.stack([t.to(dt) for t in downs]).contiguous()      # [E, h, ff]
+        if self.shared_ff:
+            self.shared_up = Linear(tensors[self.names["s_up"]])
+            self.shared_down = Linear(tensors[self.names["s_down"]])
+            if self.shared_gate:
+                self.gate_w = tensors[self.names["s_gate"]].to(self.router_w.dtype).reshape(-1).contiguous()
+
+    def kernel_libraries(self):
+        libs = ["moe"]
+        if self.shared_ff:
+            libs += self.shared_up.kernel_libraries() + self.shared_down.kernel_libraries()
+        return libs
+
+    def forward(self, x, ctx=None, sink=None):
+        T = x.shape[0]
+        ids, weights, gate = moe_ops.router(x, self.router_w, self.top, self.scoring, self.renormalize, self.gate_w)
+        pairs = T * self.top
+        tile = moe_ops.row_tile(pairs, self.E)
+        order, tile_expert = moe_ops.align(ids, self.E, tile)
+        u = torch.empty((order.numel(), self.ff), dtype=x.dtype, device=x.device)
+        moe_ops.grouped_gemm(x, self.w_up, u, order, tile_expert, pairs, self.top, tile, 0, self.activation)
+        y = torch.empty((pairs, self.hidden), dtype=x.dtype, device=x.device)
+        moe_ops.grouped_gemm(u, self.w_down, y, order, tile_expert, pairs, self.top, tile, 1, weights=weights)
+        shared = None
+        if self.shared_ff:
+            s = self.shared_up(x)
+            moe_ops.activation(s, s, self.activation)
+            shared = self.shared_down(s)
+        out = torch.empty((T, self.hidden), dtype=x.dtype, device=x.device)
+        return moe_ops.combine(y, out, self.top, shared, gate)

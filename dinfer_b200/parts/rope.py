@@ -45,7 +45,8 @@ class RotaryNeox(PositionEncoding):
         self.head_dim = int(params["head_dim"])
         self.rotary_dim = int(params.get("rotary_dim", self.head_dim))
         self.theta = float(params["theta"])
-        self.max_positions = int(params["max_positions"])
+        # the table has a row per position the engine can reach (the model's own limit may be far beyond that)
+        self.max_positions = min(int(params["max_positions"]), int(env.max_positions))
         style = params.get("style", "neox")
         if style not in ("neox", "interleaved"):
             raise ValueError(f"rotary style {style!r}: neox or interleaved")

@@ -29,6 +29,8 @@ class LayerSpec:
     mixer_norm: PartSpec
     feed_forward: PartSpec
     feed_forward_norm: PartSpec
+    # what the arrangement itself takes (tensor names of per-channel branch scales, say); see the block's class
+    extras: Mapping[str, Any] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)
