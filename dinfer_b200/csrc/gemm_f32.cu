@@ -99,6 +99,10 @@ int launch(const void* A, int64_t lda, const void* W, int64_t ldw, void* C, int6
   if (M <= 8) {
     gemm_rows_kernel<TA, TW, TC, 8><<<dim3((N + 7) / 8, 1, batch), 256, 0, stream>>>(
         (const TA*)A, lda, (const TW*)W, ldw, (TC*)C, ldc, M, N, K, sa, sw, sc);
+  } else if (M <= 32 && batch > 1) {
+    // the few rows of a decode step against many small matrices (one per head): each weight is read once
+    gemm_rows_kernel<TA, TW, TC, 32><<<dim3((N + 7) / 8, 1, batch), 256, 0, stream>>>(
+        (const TA*)A, lda, (const TW*)W, ldw, (TC*)C, ldc, M, N, K, sa, sw, sc);
   } else {
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
     if (grid.y > 65535) return refuse(DINFER_BAD_ARGUMENT, "gemm_f32: M=%d too large", M);

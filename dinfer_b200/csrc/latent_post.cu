@@ -60,7 +60,8 @@ latent_down_post_kernel(TA* __restrict__ x, int64_t ldx, const int* __restrict__
 template <typename TA>
 __global__ void __launch_bounds__(256)
 latent_q_rope_kernel(const TA* __restrict__ q, int64_t ldq, const int* __restrict__ positions,
-                     const float* __restrict__ cos_sin, int rot, TA* __restrict__ q_lat, int H, int D, int P, int R) {
+                     const float* __restrict__ cos_sin, int rot, TA* __restrict__ q_lat, int64_t ld_t, int64_t ld_h,
+                     int H, int D, int P, int R) {
   pdl_enter();
   const int t = blockIdx.x;
   const float* cs = cos_sin ? cos_sin + (int64_t)positions[t] * rot : nullptr;
@@ -75,7 +76,7 @@ latent_q_rope_kernel(const TA* __restrict__ q, int64_t ldq, const int* __restric
       const float other = to_f32<TA>(src[i ^ 1]);
       v = (i & 1) ? v * c + other * s : v * c - other * s;
     }
-    q_lat[((int64_t)t * H + h) * (R + P) + R + i] = from_f32<TA>(v);
+    q_lat[(int64_t)t * ld_t + (int64_t)h * ld_h + R + i] = from_f32<TA>(v);
   }
 }
 
@@ -102,16 +103,16 @@ DINFER_API int dinfer_latent_down_post(void* x, int64_t ldx, const int* position
   return 0;
 }
 
-// q [T, H * (D + P)] rows of stride ldq; q_lat [T, H, R + P] contiguous.
+// q [T, H * (D + P)] rows of stride ldq; q_lat [T, H, R + P] with element strides (ld_t, ld_h).
 DINFER_API int dinfer_latent_q_rope(const void* q, int64_t ldq, const int* positions, const float* cos_sin, int rot,
-                                    void* q_lat, int T, int H, int D, int P, int R, int act_dtype,
-                                    cudaStream_t stream) {
+                                    void* q_lat, int64_t ld_t, int64_t ld_h, int T, int H, int D, int P, int R,
+                                    int act_dtype, cudaStream_t stream) {
   if (T < 0 || H <= 0 || D < 0 || P < 0 || R <= 0 || rot < 0 || rot % 2 || rot > P)
     return refuse(DINFER_BAD_ARGUMENT, "latent_q_rope: bad sizes T=%d H=%d D=%d P=%d R=%d rot=%d", T, H, D, P, R, rot);
   if (T == 0 || P == 0) return 0;
   DINFER_DISPATCH_DTYPE(act_dtype, TA, {
     launch_pdl(latent_q_rope_kernel<TA>, dim3(T), dim3(256), 0, stream, (const TA*)q, ldq, positions, cos_sin, rot,
-               (TA*)q_lat, H, D, P, R);
+               (TA*)q_lat, ld_t, ld_h, H, D, P, R);
     return cuda_status("latent_q_rope");
   });
   return 0;

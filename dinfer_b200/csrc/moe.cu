@@ -213,6 +213,119 @@ moe_gemm_simt_kernel(const TA* __restrict__ A, int64_t lda, const TW* __restrict
   }
 }
 
+// ---------------------------------------------------------------- grouped product on tensor cores (bfloat16)
+// The same tiles on mma.sync m16n8k16 with 32-bit accumulation: 4 warps, tile BM x 64, K in steps of 32 through a
+// double buffer filled with cp.async (A rows gathered by pair, the expert's weight rows as they lie).  BM = 64:
+// warps 2 x 2, each 32 x 32; BM = 16 (decode steps: an expert gets a row or two): each warp 16 columns.
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+template <int BM, int MODE>
+__global__ void __launch_bounds__(128)
+moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, const __nv_bfloat16* __restrict__ Wall,
+                    __nv_bfloat16* __restrict__ C, int64_t ldc, const int* __restrict__ sorted,
+                    const int* __restrict__ tile_expert, const float* __restrict__ weights, int pairs, int top, int N,
+                    int K, int act) {
+  constexpr int BN = 64, BK = 32, LD = BK + 8;
+  constexpr int WM = BM == 64 ? 2 : 1, WN = 4 / WM;          // warps along rows and columns
+  constexpr int MTW = BM / (16 * WM), NTW = BN / (8 * WN);   // m16 and n8 tiles per warp
+  __shared__ __align__(16) __nv_bfloat16 As[2][BM][LD];
+  __shared__ __align__(16) __nv_bfloat16 Bs[2][BN][LD];
+  __shared__ int64_t src[BM];
+  __shared__ int pair_of[BM];
+  pdl_enter();
+  const int tile = blockIdx.y;
+  const int e = tile_expert[tile];
+  if (e < 0) return;
+  const int n0 = blockIdx.x * BN;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid < BM) {
+    const int p = sorted[tile * BM + tid];
+    pair_of[tid] = p;
+    src[tid] = p >= pairs ? -1 : (MODE == 0 ? (int64_t)(p / top) * lda : (int64_t)(tile * BM + tid) * lda);
+  }
+  __syncthreads();
+  const __nv_bfloat16* W = Wall + (int64_t)e * N * K;
+  auto load = [&](int k0, int buf) {
+    for (int i = tid; i < (BM + BN) * (BK / 8); i += 128) {
+      const int r = i / (BK / 8), c = (i % (BK / 8)) * 8;
+      const bool in_k = k0 + c < K;
+      if (r < BM) {
+        if (src[r] >= 0 && in_k) cp_async16(&As[buf][r][c], A + src[r] + k0 + c);
+        else *reinterpret_cast<uint4*>(&As[buf][r][c]) = make_uint4(0, 0, 0, 0);
+      } else {
+        const int n = r - BM;
+        if (n0 + n < N && in_k) cp_async16(&Bs[buf][n][c], W + (int64_t)(n0 + n) * K + k0 + c);
+        else *reinterpret_cast<uint4*>(&Bs[buf][n][c]) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    cp_async_commit();
+  };
+  const int wm = warp / WN, wn = warp % WN;
+  float acc[MTW][NTW][4];
+#pragma unroll
+  for (int i = 0; i < MTW; ++i)
+#pragma unroll
+    for (int j = 0; j < NTW; ++j)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc[i][j][q] = 0.f;
+  load(0, 0);
+  int buf = 0;
+  for (int k0 = 0; k0 < K; k0 += BK, buf ^= 1) {
+    cp_async_wait_all();
+    __syncthreads();
+    if (k0 + BK < K) load(k0 + BK, buf ^ 1);
+#pragma unroll
+    for (int kk = 0; kk < BK; kk += 16) {
+      uint32_t a[MTW][4];
+#pragma unroll
+      for (int i = 0; i < MTW; ++i)
+        ldsm_x4(a[i], &As[buf][(wm * MTW + i) * 16 + (lane & 15)][kk + ((lane >> 4) << 3)]);
+#pragma unroll
+      for (int j = 0; j < NTW; j += 2) {
+        uint32_t b[4];
+        ldsm_x4(b, &Bs[buf][(wn * NTW + j) * 8 + (lane & 7) + ((lane >> 4) << 3)][kk + (((lane >> 3) & 1) << 3)]);
+#pragma unroll
+        for (int i = 0; i < MTW; ++i) {
+          mma_bf16(acc[i][j], a[i], b[0], b[1]);
+          mma_bf16(acc[i][j + 1], a[i], b[2], b[3]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < MTW; ++i)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = (wm * MTW + i) * 16 + (lane >> 2) + half * 8;
+      const int p = pair_of[r];
+      if (p >= pairs) continue;
+      const int64_t row = MODE == 0 ? (int64_t)(tile * BM + r) : (int64_t)p;
+      const float w = MODE == 1 ? weights[p] : 1.f;
+#pragma unroll
+      for (int j = 0; j < NTW; ++j)
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const int n = n0 + (wn * NTW + j) * 8 + 2 * (lane & 3) + q;
+          const float v = acc[i][j][half * 2 + q];
+          if (n < N) C[row * ldc + n] = __float2bfloat16_rn(MODE == 0 ? activate(v, act) : v * w);
+        }
+    }
+}
+
 // ---------------------------------------------------------------- combine
 template <typename TA>
 __global__ void __launch_bounds__(256)
@@ -280,6 +393,16 @@ DINFER_API int dinfer_moe_gemm(const void* A, int64_t lda, const void* W, void* 
   if (pairs == 0) return 0;
   dim3 grid((N + 63) / 64, cap / BM);
   if (grid.y > 65535) return refuse(DINFER_BAD_ARGUMENT, "moe_gemm: too many row tiles (%d)", (int)grid.y);
+  if (act_dtype == DINFER_BF16 && w_dtype == DINFER_BF16 && K % 8 == 0 && lda % 8 == 0 &&
+      !(reinterpret_cast<uintptr_t>(A) & 15) && !(reinterpret_cast<uintptr_t>(W) & 15)) {
+#define GO_MMA(BM_, MODE_)                                                                                         \
+  launch_pdl(moe_gemm_mma_kernel<BM_, MODE_>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)A, lda,           \
+             (const __nv_bfloat16*)W, (__nv_bfloat16*)C, ldc, sorted, tile_expert, weights, pairs, top, N, K, act)
+    if (BM == 16) { if (mode == 0) GO_MMA(16, 0); else GO_MMA(16, 1); }
+    else { if (mode == 0) GO_MMA(64, 0); else GO_MMA(64, 1); }
+#undef GO_MMA
+    return cuda_status("moe_gemm");
+  }
 #define GO(BM_, MODE_)                                                                                              \
   launch_pdl(moe_gemm_simt_kernel<TA, TW, BM_, MODE_>, grid, dim3(256), 0, stream, (const TA*)A, lda, (const TW*)W, \
              (TA*)C, ldc, sorted, tile_expert, weights, pairs, top, N, K, act)

@@ -26,6 +26,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..kernels import latent_ops, ops
+from ..kernels.lib import add_launches
 from .base import MIXERS, POSITION_ENCODINGS, BuildEnv, CacheBinding, KvCacheNeed, Mixer, StepContext, build_part
 from .linear import Linear
 from .spec import PartSpec, TensorDecl
@@ -105,19 +106,35 @@ class LatentAttention(Mixer):
         latent_ops.latent_down_post(low, ctx.positions, self.q_norm_w, Rq, self.kv_norm_w if write else None, R, P,
                                     self.eps, table, cache.kv if write else None, g.slot_mapping if write else None)
         q = self.uq(low[:, :Rq])                                         # [T, H (D + P)]
-        q_lat = torch.empty((T, H, R + P), dtype=q.dtype, device=q.device)
+        # head-major storage, seen as [T, H, *]: the batched products then write whole matrices per head
+        q_lat = torch.empty((H, T, R + P), dtype=q.dtype, device=q.device).transpose(0, 1)
         self.absorb(q.view(T, H, D + P)[:, :, :D], self.uk_t, q_lat[:, :, :R])
         latent_ops.latent_q_rope(q, ctx.positions, table, q_lat, H, D, P, R)
-        o_lat = torch.empty((T, H, R), dtype=q.dtype, device=q.device)
+        o_lat = torch.empty((H, T, R), dtype=q.dtype, device=q.device).transpose(0, 1)
         self.attend(q_lat, o_lat, cache.kv, g, ctx)
         o = torch.empty((T, H, V), dtype=q.dtype, device=q.device)
         self.absorb(o_lat, self.uv, o)
         return self.o(o.view(T, H * V))
 
+    # rows up to which the per-head products run on this package's own kernel (each weight read once, 32-bit
+    # multiply-adds); beyond, bfloat16 goes to the library's batched product like the other prompt-sized products
+    OWN_ABSORB_ROWS = 32
+
     def absorb(self, a, w, out) -> None:
-        """out[:, h] = a[:, h] @ w[h]^T for every head."""
-        ops.gemm_f32_batched(a, w, out)
+        """out[:, h] = a[:, h] @ w[h]^T for every head (a [T, H, K], w [H, N, K], out [T, H, N], any strides)."""
+        if a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[0] > self.OWN_ABSORB_ROWS:
+            add_launches(1)
+            torch.bmm(a.transpose(0, 1), w.transpose(1, 2), out=out.transpose(0, 1))
+        else:
+            ops.gemm_f32_batched(a, w, out)
 
     def attend(self, q_lat, o_lat, kv, g, ctx: StepContext) -> None:
-        latent_ops.attention_latent_generic(q_lat, o_lat, kv, g.block_table, ctx.cu_seqlens, ctx.positions, self.R,
-                                            self.P, self.scale, int(self.window or 0))
+        window = int(self.window or 0)
+        if latent_ops.tc_supported(q_lat.dtype, self.R, self.P, g.block_size):
+            # inside a captured graph the longest request is whatever the engine admits
+            longest = self.env.max_positions if ctx.decode_splits else ctx.max_seq_len
+            latent_ops.attention_latent_tc(q_lat, o_lat, kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, self.R, self.P,
+                                           self.scale, window, max_q_len=ctx.max_q_len, max_seq_len=longest)
+        else:
+            latent_ops.attention_latent_generic(q_lat, o_lat, kv, g.block_table, ctx.cu_seqlens, ctx.positions, self.R,
+                                                self.P, self.scale, window)

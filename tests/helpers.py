@@ -103,7 +103,8 @@ class Replay:
     def __init__(self, model_dir: str, dtype: str, out_dir: str, max_tokens: int, extra: Sequence[str] = ()):
         self.out_dir = out_dir
         os.makedirs(out_dir, exist_ok=True)
-        self.vocab = json.load(open(os.path.join(model_dir, "config.json")))["vocab_size"]
+        cfg = json.load(open(os.path.join(model_dir, "config.json")))
+        self.vocab = cfg["vocab_size"] if "vocab_size" in cfg else cfg["vocab"]
         self.proc = subprocess.Popen(
             [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype,
              "--out", out_dir, "--max-tokens", str(max_tokens), *extra],
@@ -283,7 +284,7 @@ class LocalReplay:
         from dinfer_b200.config.engine_config import EngineConfig
         from dinfer_b200.engine.runner import ModelRunner
         cfg = json.load(open(os.path.join(model_dir, "config.json")))
-        self.vocab = cfg["vocab_size"]
+        self.vocab = cfg["vocab_size"] if "vocab_size" in cfg else cfg["vocab"]
         n = (max_tokens + 63) // 64 * 64
         self.runner = ModelRunner.from_dir(model_dir, EngineConfig(
             max_model_len=min(n, cfg.get("max_position_embeddings", cfg.get("max_positions", n))), max_num_seqs=16,

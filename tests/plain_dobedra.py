@@ -76,16 +76,30 @@ def relu2_expert(h, up, down):
     return (torch.relu(h @ up.T) ** 2) @ down.T
 
 
-def moe_ff(h, t, mlp: dict):
+def router_margin(z, top):
+    """How far the router's choice is from going the other way: the gap between the ``top``-th and the next logit
+    (infinite when every expert is chosen)."""
+    if top >= z.shape[-1]:
+        return torch.full(z.shape[:-1], float("inf"), dtype=z.dtype)
+    v = torch.sort(z, dim=-1, descending=True).values
+    return v[..., top - 1] - v[..., top]
+
+
+def moe_ff(h, t, mlp: dict, margins=None):
+    """``margins`` (a list) receives each token's ``router_margin``."""
     E, top = mlp["router"]["experts"], mlp["router"]["top"]
     z = h @ t["router"].T
+    if margins is not None:
+        margins.append(router_margin(z, top))
     s = torch.softmax(z, dim=-1)
     w, idx = torch.topk(s, top, dim=-1)
     out = torch.zeros_like(h)
-    for tok in range(h.shape[0]):
-        for k in range(top):
-            e = int(idx[tok, k])
-            out[tok] += w[tok, k] * relu2_expert(h[tok:tok + 1], t[f"e{e}.up"], t[f"e{e}.down"])[0]
+    for e in range(E):
+        chose = (idx == e)                                               # [T, top]
+        rows = chose.any(-1).nonzero().flatten()
+        if rows.numel():
+            weight = (w * chose)[rows].sum(-1, keepdim=True)
+            out[rows] += weight * relu2_expert(h[rows], t[f"e{e}.up"], t[f"e{e}.down"])
     if mlp.get("shared"):
         g = torch.sigmoid(h @ t["shared.sg"].T)                            # [T, 1]
         out = out + g * relu2_expert(h, t["shared.up"], t["shared.down"])
@@ -96,8 +110,10 @@ def sub(tensors, prefix):
     return {k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)}
 
 
-def forward(config: dict, tensors: Dict[str, torch.Tensor], tokens: List[int], dtype=torch.float64, streams=None):
-    """Logits [T, vocab] of one sequence; ``streams`` (a list) receives the residual after every layer."""
+def forward(config: dict, tensors: Dict[str, torch.Tensor], tokens: List[int], dtype=torch.float64, streams=None,
+            margins=None):
+    """Logits [T, vocab] of one sequence; ``streams`` (a list) receives the residual after every layer, ``margins``
+    (a list) the router margins [T] of every routed layer."""
     W = {k: v.to(dtype) for k, v in tensors.items()}
     eps = config["norm"]["eps"]
     pos = torch.arange(len(tokens))
@@ -109,7 +125,6 @@ def forward(config: dict, tensors: Dict[str, torch.Tensor], tokens: List[int], d
         if layer["type"] != "latent_attention":
             raise ValueError(layer["type"])
         h1 = layer_norm(x, W[pre + "norm1"], W[pre + "norm1.b"], eps)
-        h2 = layer_norm(x, W[pre + "norm2"], W[pre + "norm2.b"], eps)
         mix = sub(W, pre + "mix.")
         if "kv_from" in m and m["kv_from"] is not None:
             c, kr = kept[m["kv_from"]]
@@ -118,7 +133,8 @@ def forward(config: dict, tensors: Dict[str, torch.Tensor], tokens: List[int], d
         y = latent_attention(h1, pos, c, kr, mix, m, eps) * W[pre + "ls1"]
         if layer.get("mlp"):
             f = sub(W, pre + "mlp.")
-            ff = dense_ff(h2, f) if layer["mlp"]["kind"] == "dense" else moe_ff(h2, f, layer["mlp"])
+            h2 = layer_norm(x, W[pre + "norm2"], W[pre + "norm2.b"], eps)
+            ff = dense_ff(h2, f) if layer["mlp"]["kind"] == "dense" else moe_ff(h2, f, layer["mlp"], margins)
             y = y + ff * W[pre + "ls2"]
         x = x + y
         if streams is not None:

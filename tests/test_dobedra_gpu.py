@@ -1,0 +1,380 @@
+"""Dobedra on the device against the plain implementation (``plain_dobedra.py``): every mechanism alone, then whole
+models replayed whole, with a decoded tail, in portions down to two tokens and mixed with few pages, then greedy
+generation through the entry point."""
+import json
+import math
+import os
+import random
+
+import numpy as np
+import pytest
+import torch
+
+import dobedra_cases as C
+import helpers as H
+import plain_dobedra as P
+
+pytestmark = pytest.mark.gpu
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+TOL = {"float32": 2e-5, "bfloat16": 2e-2}
+
+
+def dev(t, dt=None):
+    return t.to("cuda", dt) if dt is not None else t.to("cuda")
+
+
+def close(got, want, tol):
+    want = want.double().cpu()
+    err = float((got.double().cpu() - want).abs().max() / max(1e-9, float(want.abs().max())))
+    assert err <= tol, f"relative error {err:.3e} above {tol}"
+
+
+# ---------------------------------------------------------------- mechanisms alone
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("h", [72, 256, 1000])
+def test_layer_norm_with_pending_branches_and_two_outputs(dtype, h):
+    from dinfer_b200.kernels import ops
+    dt = DT[dtype]
+    g = torch.Generator().manual_seed(h)
+    T = 7
+    x = torch.randn(T, h, generator=g) * 3 + 1.5
+    d1, d2 = (torch.randn(T, h, generator=g).to(dt) for _ in range(2))
+    s1, s2, w1, b1, w2, b2 = (torch.randn(h, generator=g).to(dt) for _ in range(6))
+    v = x.double() + d1.double() * s1.double() + d2.double() * s2.double()
+    res = dev(x.clone())
+    o1 = torch.empty(T, h, dtype=dt, device="cuda")
+    o2 = torch.empty_like(o1)
+    ops.layernorm(res, dev(w1), dev(b1), 1e-5, o1, deltas=[(dev(d1), dev(s1)), (dev(d2), dev(s2))], weight2=dev(w2),
+                  bias2=dev(b2), out2=o2)
+    close(res, v, 1e-6)                                        # the sum is written back in 32-bit
+    close(o1, P.layer_norm(v, w1.double(), b1.double(), 1e-5), TOL[dtype] / 2)
+    close(o2, P.layer_norm(v, w2.double(), b2.double(), 1e-5), TOL[dtype] / 2)
+    # gathered rows, one delta without a scale, no write-back
+    rows = torch.tensor([5, 0, 5, 2], dtype=torch.int32)
+    res2 = dev(x.clone())
+    o3 = torch.empty(4, h, dtype=dt, device="cuda")
+    ops.layernorm(res2, dev(w1), None, 1e-5, o3, deltas=[(dev(d1), None)], rows=dev(rows))
+    assert torch.equal(res2.cpu(), x)
+    close(o3, P.layer_norm((x.double() + d1.double())[rows.long()], w1.double(), torch.zeros(h).double(), 1e-5), TOL[dtype] / 2)
+    # the same sum by the kernel that only adds
+    res3 = dev(x.clone())
+    ops.scaled_add(res3, [(dev(d1), dev(s1)), (dev(d2), dev(s2))])
+    close(res3, v, 1e-6)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("sizes", [(3, 16, 16, 32, 40, 16), (2, 12, 6, 24, 20, 4), (1, 64, 32, 128, 48, 32)])
+def test_latent_rows_into_the_cache_and_query_rotation(dtype, sizes):
+    from dinfer_b200.kernels import latent_ops
+    from dinfer_b200.parts.rope import rope_table
+    H_, D, Pd, R, Rq, rot = sizes
+    dt = DT[dtype]
+    g = torch.Generator().manual_seed(sum(sizes))
+    T, page, pages, base, eps = 11, 4, 9, 300.0, 1e-5
+    low = torch.randn(T, Rq + R + Pd, generator=g).to(dt)
+    wq, wkv = (torch.rand(Rq, generator=g) + 0.5).to(dt), (torch.rand(R, generator=g) + 0.5).to(dt)
+    pos = torch.tensor([0, 1, 2, 3, 4, 5, 6, 40, 41, 63, 17], dtype=torch.int32)
+    slots = torch.randperm(page * pages, generator=g)[:T].to(torch.int32)
+    slots[3] = -1                                              # a token without a place writes nothing
+    table = rope_table(rot, base, 64, "cuda")
+    cache = torch.full((pages, 1, 1, page, R + Pd), 777.0, dtype=dt, device="cuda")
+    x = dev(low.clone())
+    latent_ops.latent_down_post(x, dev(pos), dev(wq), Rq, dev(wkv), R, Pd, eps, table, cache, dev(slots))
+    rotd = {"base": base, "dims": rot}
+    close(x[:, :Rq], P.rms_norm(low[:, :Rq].double(), wq.double(), eps), TOL[dtype] / 2)
+    c = P.rms_norm(low[:, Rq:Rq + R].double(), wkv.double(), eps)
+    kr = P.rotate_pairs(low[:, Rq + R:].double(), pos, base, rot)
+    flat = cache.view(-1, R + Pd).cpu()
+    for t in range(T):
+        if slots[t] < 0:
+            continue
+        close(flat[slots[t], :R], c[t], TOL[dtype] / 2)
+        close(flat[slots[t], R:], kr[t], TOL[dtype] / 2)
+    untouched = torch.ones(page * pages, dtype=torch.bool)
+    untouched[slots[slots >= 0].long()] = False
+    assert (flat[untouched] == 777.0).all()
+    # the query side: the last P of every head, rotated, behind R elements that are left alone
+    q = torch.randn(T, H_ * (D + Pd), generator=g).to(dt)
+    q_lat = torch.full((T, H_, R + Pd), 5.0, dtype=dt, device="cuda")
+    latent_ops.latent_q_rope(dev(q), dev(pos), table, q_lat, H_, D, Pd, R)
+    want = P.rotate_pairs(q.double().view(T, H_, D + Pd)[..., D:], pos, base, rot)
+    close(q_lat[..., R:], want, TOL[dtype] / 2)
+    assert (q_lat[..., :R] == 5.0).all()
+
+
+def plain_latent_scores(q_lat, rows, R, scale, pos):
+    """softmax(q . rows_j * scale over j <= pos) rows_j[:R] for one query [H, R + P] and keys [n, R + P]."""
+    s = (q_lat.double() @ rows.double().T) * scale
+    s[:, pos + 1:] = float("-inf")
+    return torch.softmax(s, -1) @ rows.double()[:, :R]
+
+
+def scatter_into_pages(rows, page, rng, spare=3):
+    """Keys of one request put into shuffled pages: (cache [pages, 1, 1, page, W], table row)."""
+    n, W = rows.shape
+    need = (n + page - 1) // page
+    ids = list(range(need + spare))
+    rng.shuffle(ids)
+    cache = torch.full((need + spare, 1, 1, page, W), float("nan"), dtype=rows.dtype)
+    for j in range(n):
+        cache[ids[j // page], 0, 0, j % page] = rows[j]
+    return cache, ids[:need]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("kernel", ["generic", "tc"])
+@pytest.mark.parametrize("sizes", [(4, 32, 16, 16), (6, 64, 32, 8), (16, 128, 64, 32), (3, 48, 16, 4)])
+def test_latent_attention_far_keys_page_borders_and_the_causal_edge(dtype, kernel, sizes):
+    """One request of 700 cached rows in shuffled pages.  Among hundreds of small scores one key stands out for each
+    query: a far one (position 2), the one on each side of a page border, the query's own position; the row just
+    behind the query's position carries a huge score and must not be seen.  Decoded tokens (one query of a request)
+    and a portion of a prompt run in the same launch."""
+    from dinfer_b200.kernels import latent_ops
+    Hh, R, Pd, page = sizes
+    if kernel == "tc" and (dtype != "bfloat16" or not latent_ops.tc_supported(DT[dtype], R, Pd, page)):
+        pytest.skip("the tensor-core kernel takes bfloat16 and sizes in multiples of 16")
+    dt = DT[dtype]
+    rng = random.Random(R + Pd)
+    g = torch.Generator().manual_seed(R * 7 + Pd)
+    n, W, scale = 700, R + Pd, 0.3
+    rows = (torch.randn(n, W, generator=g) * 0.2).to(dt)
+    stand_out = {2: 2, 331: 320 - (320 % page) - 1, 402: 400 - (400 % page), 555: 555, 699: 17, 640: 639}
+    qpos = [640, 2, 331, 402, 555, 699]                       # the order of the queries in the batch
+    marks = torch.linalg.qr(torch.randn(W, len(qpos), generator=g)).Q.T.contiguous()      # orthonormal rows
+    for i, p in enumerate(qpos):
+        rows[stand_out[p]] += (marks[i] * 3.0).to(dt)
+        if p + 1 < n:
+            rows[p + 1] += (marks[i] * 30.0).to(dt)           # just behind the causal edge
+    # request 0: a portion of 3 tokens at positions 638..640 (the last one marked); requests 1..5: single tokens
+    q_all, pos_all, cu, tables, seqs = [], [], [0], [], []
+    cache, table = scatter_into_pages(rows, page, rng)
+    for i, p in enumerate(qpos):
+        lo = p - 2 if i == 0 else p
+        for pp in range(lo, p + 1):
+            qv = torch.randn(Hh, W, generator=g) * 0.1
+            if pp == p:
+                qv += marks[i] * torch.linspace(11.0, 15.0, Hh)[:, None]
+            q_all.append(qv)
+            pos_all.append(pp)
+        cu.append(len(q_all))
+        tables.append(table)
+        seqs.append(p + 1)
+    q_lat = torch.stack(q_all).to(dt)
+    width = max(len(t) for t in tables) + 2
+    bt = torch.full((len(tables), width), -1, dtype=torch.int32)
+    for i, t in enumerate(tables):
+        bt[i, :len(t)] = torch.tensor(t, dtype=torch.int32)
+    out = torch.full((len(q_all), Hh, R), float("nan"), dtype=dt, device="cuda")
+    args = (dev(q_lat), out, dev(cache), dev(bt), dev(torch.tensor(cu, dtype=torch.int32)))
+    if kernel == "generic":
+        latent_ops.attention_latent_generic(*args, dev(torch.tensor(pos_all, dtype=torch.int32)), R, Pd, scale)
+    else:
+        latent_ops.attention_latent_tc(*args, dev(torch.tensor(seqs, dtype=torch.int32)), R, Pd, scale,
+                                       max_q_len=3, max_seq_len=n)
+    for t, p in enumerate(pos_all):
+        want = plain_latent_scores(q_lat[t], rows, R, scale, p)
+        close(out[t], want, TOL[dtype])
+    # the marked queries really rest on their one key
+    for i, p in enumerate(qpos):
+        t = cu[i + 1] - 1
+        w = torch.softmax((q_lat[t].double() @ rows.double().T * scale)[:, :p + 1], -1)
+        assert float(w[:, stand_out[p]].min()) > 0.5
+
+
+MOE_CASES = [dict(E=5, top=1, ff=24, shared=40), dict(E=8, top=3, ff=16, shared=0), dict(E=1, top=1, ff=32, shared=8),
+             dict(E=16, top=4, ff=64, shared=96), dict(E=7, top=7, ff=20, shared=12)]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("case", MOE_CASES)
+def test_routed_feed_forward_against_plain_and_alone_against_batched(dtype, case):
+    from dinfer_b200.parts.base import BuildEnv, FEED_FORWARDS
+    from dinfer_b200.parts import moe  # noqa: F401
+    dt = DT[dtype]
+    h = 64 if case["ff"] % 8 == 0 else 72
+    g = torch.Generator().manual_seed(case["E"] * 10 + case["top"])
+    params = {"num_experts": case["E"], "top_k": case["top"], "expert_size": case["ff"], "shared_size": case["shared"],
+              "activation": "relu2", "scoring": "softmax", "renormalize": False, "shared_gate": "sigmoid",
+              "router": "router", "expert_up": "e{e}.up", "expert_down": "e{e}.down", "shared_up": "shared.up",
+              "shared_down": "shared.down", "shared_gate_proj": "shared.sg"}
+    part = FEED_FORWARDS.get("moe")(params, BuildEnv(torch.device("cuda"), dt, h, 64), "m.")
+    W = {}
+    for d in part.declare():
+        t = torch.randn(d.shape, generator=g) * (1.5 if d.name.endswith("router") else 0.15)
+        W[d.name] = t.to(dt)
+    part.bind({k: dev(v) for k, v in W.items()})
+    plain = {k[2:]: v.double() for k, v in W.items()}
+    mlp = {"router": {"experts": case["E"], "top": case["top"]}, "shared": {"ff": case["shared"]} if case["shared"] else None}
+    for T in (1, 3, 37, 150):
+        x = torch.randn(4 * T + 8, h, generator=g).to(dt)
+        # rows whose choice of experts is decided (a gap to the first rejected expert that rounding cannot close)
+        x = x[P.router_margin(x.double() @ plain["router"].T, case["top"]) > 0.2][:T]
+        assert x.shape[0] == T
+        got = part.forward(dev(x))
+        close(got, P.moe_ff(x.double(), plain, mlp), TOL[dtype])
+        if T == 37:                                            # a token's row does not depend on its company
+            for t in (0, 17, 36):
+                alone = part.forward(dev(x[t:t + 1].clone()))
+                close(alone[0], got[t], 1e-6 if dtype == "float32" else 1e-2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_router_choices_weights_and_gate(dtype):
+    from dinfer_b200.kernels import moe_ops
+    dt = DT[dtype]
+    g = torch.Generator().manual_seed(5)
+    T, K, E, top = 50, 96, 11, 4
+    x, wr, wg = torch.randn(T, K, generator=g).to(dt), torch.randn(E, K, generator=g).to(dt), torch.randn(K, generator=g).to(dt)
+    s = torch.softmax(x.double() @ wr.double().T, -1)
+    w, idx = torch.topk(s, top, -1)
+    ids, weights, gate = moe_ops.router(dev(x), dev(wr), top, "softmax", False, dev(wg))
+    assert torch.equal(ids.cpu().long(), idx)
+    close(weights, w, 1e-5)
+    close(gate, torch.sigmoid(x.double() @ wg.double()), 1e-5)
+    _, w2, _ = moe_ops.router(dev(x), dev(wr), top, "softmax", True)
+    close(w2, w / w.sum(-1, keepdim=True), 1e-5)
+    wr = (wr.float() * 0.05).to(dt)                            # sigmoids that do not saturate into ties
+    ids3, w3, _ = moe_ops.router(dev(x), dev(wr), top, "sigmoid", False)
+    w3p, idx3 = torch.topk(torch.sigmoid(x.double() @ wr.double().T), top, -1)
+    assert torch.equal(ids3.cpu().long(), idx3)
+    close(w3, w3p, 1e-5)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("rows", [1, 20, 40, 600])
+def test_gated_feed_forward_with_the_tanh_gelu(dtype, rows):
+    from dinfer_b200.models import decoder  # noqa: F401  (registers the parts)
+    from dinfer_b200.parts.base import BuildEnv, FEED_FORWARDS
+    dt = DT[dtype]
+    h, ff = 64, 96
+    g = torch.Generator().manual_seed(rows)
+    part = FEED_FORWARDS.get("gated_mlp")({"intermediate_size": ff, "activation": "gelu_tanh", "gate_proj": "gate",
+                                           "up_proj": "up", "down_proj": "down"},
+                                          BuildEnv(torch.device("cuda"), dt, h, 64), "f.")
+    W = {d.name: (torch.randn(d.shape, generator=g) * 0.3).to(dt) for d in part.declare()}
+    part.bind({k: dev(v) for k, v in W.items()})
+    x = (torch.randn(rows, h, generator=g) * 2).to(dt)
+    close(part.forward(dev(x)), P.dense_ff(x.double(), {k[2:]: v.double() for k, v in W.items()}), TOL[dtype])
+
+
+# ---------------------------------------------------------------- whole models
+
+LENGTHS = {"A": {"a": 1, "b": 2, "c": 19, "d": 64, "e": 97, "f": 333},
+           "B": {"a": 3, "b": 16, "c": 17, "d": 63, "e": 150, "f": 401},
+           "C": {"a": 2, "b": 33, "c": 129, "d": 260}}
+
+
+class Oracle:
+    def __init__(self, model_dir):
+        self.cfg = json.load(open(os.path.join(model_dir, "config.json")))
+        self.W = C.load_weights(model_dir)
+
+    def logits(self, ids):
+        return P.forward(self.cfg, self.W, list(ids)).numpy()
+
+
+@pytest.fixture(scope="module")
+def model_dirs(tmp_path_factory):
+    out = {}
+    for name, cfg in C.CONFIGS.items():
+        for dt in DT:
+            out[(name, dt)] = C.write_model(str(tmp_path_factory.mktemp(f"dobedra{name}_{dt}")), cfg, 11 + ord(name), DT[dt])
+    # the 32-bit folders hold the bfloat16 values, widened: one set of requests and expected logits serves both
+    return out
+
+
+_REQUESTS = {}
+
+
+def decided_requests(name, model_dirs):
+    """The requests of ``LENGTHS[name]`` (tokens that leave no router undecided, see ``decided_tokens``) and the plain
+    implementation's logits for them; made once per configuration (both dtypes hold the same bfloat16 values)."""
+    if name not in _REQUESTS:
+        cfg, rng = C.CONFIGS[name], random.Random(7 + ord(name))
+        oracle = Oracle(model_dirs[(name, "bfloat16")])
+        tokens = {r: C.decided_tokens(cfg, oracle.W, n, rng) for r, n in LENGTHS[name].items()}
+        _REQUESTS[name] = (tokens, {r: oracle.logits(t) for r, t in tokens.items()})
+    return _REQUESTS[name]
+
+
+@pytest.mark.parametrize("block_size", [4, 16, 64])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_replay_all_ways(model_dirs, name, dtype, block_size):
+    """Every position of every request, whole / with a decoded tail long enough to pass page borders / in portions
+    down to two tokens / mixed with up to four live requests on a pool that only holds the most demanding step, so
+    that pages are freed and used again; pages of 4, 16 and 64 tokens."""
+    model_dir = model_dirs[(name, dtype)]
+    cfg = C.CONFIGS[name]
+    rng = random.Random(99 + ord(name))
+    lengths = LENGTHS[name]
+    tokens, want = decided_requests(name, model_dirs)
+    schedules = {
+        "whole": H.schedule_whole(lengths),
+        "tail": H.schedule_tail(lengths, 70),
+        "chunks": H.schedule_chunks(lengths, rng),
+        "mixed": H.schedule_mixed(lengths, rng),
+        "mixed2": H.schedule_mixed(dict(reversed(list(lengths.items()))), rng, max_live=3, decode_tail=40),
+    }
+    max_tokens = max(H.max_live_tokens(s, round_to=max(64, block_size)) for s in schedules.values())
+    rp = H.LocalReplay(model_dir, dtype, max_tokens, block_size=block_size)
+    worst = {}
+    for sname, steps in schedules.items():
+        got = H.run_schedule(rp, steps, tokens, tag=sname + "/")
+        worst[sname] = max(H.rel_err(got[r], want[r]) for r in tokens)
+    assert rp.close() == 0
+    tol = H.TOLERANCE[dtype]
+    bad = {k: v for k, v in worst.items() if not v <= tol}
+    assert not bad, f"{name} {dtype} pages of {block_size}: relative error above {tol}: {bad} (all: {worst})"
+
+
+def test_trace_runner_and_first_tokens(model_dirs, tmp_path):
+    """Through ``bin/trace_run`` as a process: the first tokens of sequences (a request of one token, the first two
+    positions of others), and a request that sits steps out while others come and go."""
+    model_dir = model_dirs[("A", "float32")]
+    cfg = C.CONFIGS["A"]
+    rng = random.Random(5)
+    tokens = {r: H.random_tokens(rng, n, cfg["vocab"]) for r, n in {"p": 1, "q": 2, "r": 70, "s": 45}.items()}
+    oracle = Oracle(model_dir)
+    rp = H.Replay(model_dir, "float32", str(tmp_path / "out"), 256)
+    try:
+        a = rp.step([{"id": "p", "tokens": tokens["p"], "want": [0]}, {"id": "r", "tokens": tokens["r"][:2], "want": [0, 1]}], ["p"])
+        b = rp.step([{"id": "q", "tokens": tokens["q"], "want": [0, 1]}, {"id": "s", "tokens": tokens["s"][:40], "want": [39]}], ["q"])
+        c = rp.step([{"id": "r", "tokens": tokens["r"][2:], "want": [67]}, {"id": "s", "tokens": tokens["s"][40:41], "want": [0]}], ["r"])
+        d = rp.step([{"id": "s", "tokens": tokens["s"][41:], "want": [3]}], ["s"])
+    finally:
+        assert rp.close() == 0
+    for got, want in ((a[0], oracle.logits(tokens["p"])[0]), (a[1:], oracle.logits(tokens["r"])[:2]),
+                      (b[:2], oracle.logits(tokens["q"])), (b[2], oracle.logits(tokens["s"])[39]),
+                      (c[0], oracle.logits(tokens["r"])[69]), (c[1], oracle.logits(tokens["s"])[40]),
+                      (d[0], oracle.logits(tokens["s"])[44])):
+        assert H.rel_err(np.asarray(got), np.asarray(want)) <= H.TOLERANCE["float32"]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_through_the_entry_point(model_dirs, name, dtype):
+    """``LLM.generate``: scheduler, chunked prompts (a token budget below the prompts' lengths), decode steps replayed
+    as CUDA graphs, greedy sampling; more requests than run at once.  Every generated token is the plain
+    implementation's choice over the very sequence the engine produced (or a near-tie in reduced precision)."""
+    from dinfer_b200 import LLM, SamplingParams
+    model_dir = model_dirs[(name, dtype)]
+    cfg = C.CONFIGS[name]
+    rng = random.Random(21)
+    prompts = [H.random_tokens(rng, n, cfg["vocab"]) for n in (1, 5, 23, 40, 9, 31)]
+    llm = LLM(model_dir, dtype=dtype, max_model_len=128, max_num_seqs=4, max_num_batched_tokens=16, block_size=16,
+              num_blocks=40)
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True))
+    oracle = Oracle(model_dir)
+    exact = total = 0
+    for p, o in zip(prompts, outs):
+        assert len(o.output_ids) == 40
+        lg = oracle.logits(list(p) + list(o.output_ids))
+        exact += sum(int(lg[len(p) - 1 + i].argmax()) == t for i, t in enumerate(o.output_ids))
+        total += 40
+    # 32-bit: the plain implementation's own choice throughout; bfloat16: all but near-ties of two logits and the rare
+    # token whose router sat between two experts
+    assert exact >= (0.9 if dtype == "bfloat16" else 0.99) * total, (exact, total)
+    assert llm.runner.split_norms_buckets() == [] and any(isinstance(k, int) for k in llm.runner._graphs)
