@@ -330,6 +330,116 @@ def closed_loop_run(shape: str, clients: int, prompt_len: int, output_len: int, 
     return 0
 
 
+# ---------------------------------------------------------------- Dobedra beside Qwen3 at equal layer sizes
+def _dobedra_cfg(width, heads, dim, rot, vdim, kv_rank, q_rank, dense_ff, experts, top, ff, shared, vocab=32768):
+    m = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "kv_rank": kv_rank, "q_rank": q_rank,
+         "rot": {"base": 10000.0, "dims": rot}, "scale": (dim + rot) ** -0.5}
+    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}, "shared": {"ff": shared}}
+    layers = [{"type": "latent_attention", "mixer": m, "mlp": {"kind": "dense", "ff": dense_ff}},
+              {"type": "latent_attention", "mixer": m, "mlp": moe},
+              {"type": "latent_attention", "mixer": m, "mlp": moe},
+              {"type": "latent_attention", "mixer": dict(m, kv_from=2), "mlp": moe}]
+    return {"architecture": "Dobedra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+            "layers": layers}
+
+
+def _qwen3_cfg(width, heads, kv_heads, head_dim, inter, vocab=32768):
+    return dict(QWEN3_8B, vocab_size=vocab, hidden_size=width, intermediate_size=inter, num_hidden_layers=4,
+                num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=head_dim)
+
+
+# layer sizes that resemble real models of the design's kind (a latent of 512 + 64 under 16 or 32 heads of 128 + 64,
+# 64 experts of which a token uses 6, a shared expert), and a smaller one; beside each the dense Qwen3 layer of the same
+# width and head count whose feed-forward has about the weights a Dobedra token uses
+DESIGN_SIZES = {
+    "small": (_dobedra_cfg(1024, 8, 64, 32, 64, 256, 512, 4096, 16, 2, 512, 1024), _qwen3_cfg(1024, 8, 2, 128, 2048)),
+    "medium": (_dobedra_cfg(2048, 16, 128, 64, 128, 512, 1536, 10944, 64, 6, 1408, 2816), _qwen3_cfg(2048, 16, 4, 128, 7680)),
+    "large": (_dobedra_cfg(4096, 32, 128, 64, 128, 512, 1536, 12288, 64, 6, 2048, 4096), _qwen3_cfg(4096, 32, 8, 128, 12288)),
+}
+
+
+def _time_model(cfg, batch, context, prefill_tokens, steps, seed=5, profile=None):
+    """(prefill ms of one prompt, decode ms per step of ``batch`` requests at ``context``, launches per decode step) of
+    four layers of ``cfg`` with random weights: the prompt through the step function (best of three), the decode
+    step as its captured graph replayed ``steps`` times between CUDA events."""
+    import torch
+    from dinfer_b200.config.engine_config import EngineConfig
+    from dinfer_b200.engine.batch import StepEntry
+    from dinfer_b200.engine.runner import ModelRunner
+    from dinfer_b200.kernels import lib
+    from dinfer_b200.weights.random_init import RandomSource
+    vocab = cfg.get("vocab_size", cfg.get("vocab"))
+    longest = max(context, prefill_tokens) + 64
+    eng = EngineConfig(max_model_len=longest, max_num_seqs=batch, max_num_batched_tokens=max(2048, prefill_tokens),
+                       num_blocks=(batch + 1) * ((longest + 15) // 16) + 8, block_size=16, dtype="bfloat16",
+                       mixed_cuda_graph=False)
+    runner = ModelRunner(cfg, RandomSource(cfg, seed, std=0.02, norm_jitter=0.0), eng)
+    rng = random.Random(seed)
+    pre = None
+    for i in range(4):
+        ids = [rng.randrange(vocab) for _ in range(prefill_tokens)]
+        torch.cuda.synchronize()
+        if profile == "prefill" and i == 3:
+            torch.cuda.profiler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        runner.step([StepEntry(("p", i), ids, [prefill_tokens - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        if profile == "prefill" and i == 3:
+            torch.cuda.profiler.stop()
+        runner.finish(("p", i))
+        if i > 0:
+            pre = e0.elapsed_time(e1) if pre is None else min(pre, e0.elapsed_time(e1))
+    for b in range(batch):                                     # fill the cache up to the context, one request a step
+        runner.step([StepEntry(b, [rng.randrange(vocab) for _ in range(context - 4)], [])])
+    for _ in range(3):
+        runner.step([StepEntry(b, [rng.randrange(vocab)], [0]) for b in range(batch)])
+    torch.cuda.synchronize()
+    if profile == "decode":
+        runner._graph_ok = False
+        torch.cuda.profiler.start()
+        runner.step([StepEntry(b, [rng.randrange(vocab)], [0]) for b in range(batch)])
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        return pre, 0.0, 0
+    l0 = lib.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    runner.replay_last_decode(steps)
+    e1.record()
+    torch.cuda.synchronize()
+    dec = e0.elapsed_time(e1) / steps
+    launches = (lib.launch_count() - l0) // steps
+    del runner
+    torch.cuda.empty_cache()
+    return pre, dec, launches
+
+
+def design_run(a) -> int:
+    """``--design dobedra``: prefill and decode throughput of four Dobedra layers beside four Qwen3 layers of the same
+    width and head count, at the sizes of ``DESIGN_SIZES``; one JSON line."""
+    rows = {}
+    sizes = [a.design_size] if a.design_size else list(DESIGN_SIZES)
+    for name in sizes:
+        ours, theirs = DESIGN_SIZES[name]
+        row = {}
+        for label, cfg in (("dobedra", ours), ("qwen3", theirs)):
+            if a.profile and label != (a.design_model or "dobedra"):
+                continue
+            pre, dec, launches = _time_model(cfg, a.batch, a.context, PREFILL_TOKENS, a.steps, profile=a.profile)
+            row[label] = {"prefill_ms": round(pre, 3), "prefill_tok_s": round(PREFILL_TOKENS * 1e3 / pre, 1),
+                          "decode_ms_per_step": round(dec, 4), "decode_tok_s": round(a.batch * 1e3 / dec, 1) if dec else None,
+                          "launches_per_decode_step": launches}
+        rows[name] = row
+    if a.profile:
+        return 0
+    print(json.dumps({"metric": "Dobedra beside Qwen3, four layers at equal width and heads (bf16, random weights): "
+                                f"prefill of {PREFILL_TOKENS} tokens, decode at batch {a.batch} context {a.context}",
+                      "sizes": rows, "steps": a.steps, "impl": "ours", "data": "synthetic"}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
@@ -349,6 +459,11 @@ def main() -> int:
     ap.add_argument("--closed-loop", default=None, metavar="C,P,O",
                     help="the reference's serving measurement at engine level instead: C clients, each sending its "
                          "next request when the last has ended, prompts of P tokens, O generated tokens (--shape applies)")
+    ap.add_argument("--design", choices=["dobedra"], default=None,
+                    help="instead of the benchmark: four layers of this design beside four Qwen3 layers of equal width, "
+                         "prefill and decode, at a few layer sizes")
+    ap.add_argument("--design-size", choices=["small", "medium", "large"], default=None, help="only this size")
+    ap.add_argument("--design-model", choices=["dobedra", "qwen3"], default=None, help="with --profile: which of the two")
     a = ap.parse_args()
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -360,6 +475,10 @@ def main() -> int:
         return 2
     a.warmup = max(a.warmup, 3)
     import torch
+    if a.design:
+        if a.context == 4096:
+            a.context = 2048
+        return design_run(a)
     if a.profile:
         return profile_region(a)
     if a.serving:

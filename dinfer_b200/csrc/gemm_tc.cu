@@ -47,7 +47,8 @@ struct GemmParams {
   void* out; int64_t ldc;        // [tokens, N] row-major, bf16 or f32
   int tokens, N, K;
   int k_blocks_per_split, splits;
-  int act;                       // 1: weight rows come in (gate, up) pairs and out[t, j] = silu(gate_j) * up_j, N / 2 wide
+  int act;                       // > 0: weight rows come in (gate, up) pairs and out[t, j] = g(gate_j) * up_j, N / 2 wide;
+                                 // g = silu (1) or the tanh form of gelu (2)
   // residual mode (decode orientation): the product is added into resid [tokens, ldr] (f32) and out gets the new
   // residual times norm_w, rounded; the sums of squares of the rows this CTA owns go to ss_out[part][token]
   float* resid; int64_t ldr;
@@ -152,6 +153,11 @@ __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + 
 // the prompt epilogue's: fast exponential and division, as the reference's gate kernel has them
 // (crates/kernels/cuda/common.cuh:55); the quotient is 0 where 1 + e^-g passes 2^126, as is its limit
 __device__ __forceinline__ float silu_mul_fast(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
+// the tanh form of gelu as a gate: 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))) * u
+__device__ __forceinline__ float gelu_tanh_mul(float g, float u) {
+  return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+}
+__device__ __forceinline__ float gate_mul(float g, float u, int act) { return act == 2 ? gelu_tanh_mul(g, u) : silu_mul(g, u); }
 
 template <int N_TILE> constexpr int tmem_cols() { return N_TILE <= 32 ? 32 : (N_TILE <= 64 ? 64 : (N_TILE <= 128 ? 128 : 256)); }
 // Rows of the tile that one CTA of a split-K cluster owns, and the floats of its receive buffer
@@ -326,7 +332,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               const float g = __uint_as_float(v[j]);
               const float u = __shfl_down_sync(0xffffffffu, g, 1);
               if (!(lane & 1) && n + 1 < p.N && b0 + c0 + j < p.tokens)
-                out[(int64_t)(b0 + c0 + j) * p.ldc + (n >> 1)] = out_cast<OutT>(silu_mul(g, u));
+                out[(int64_t)(b0 + c0 + j) * p.ldc + (n >> 1)] = out_cast<OutT>(gate_mul(g, u, p.act));
             }
           } else if (!clustered) {
             if (n < p.N) {
@@ -416,7 +422,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
           if (p.ss_in) { g *= s_rstd[c]; u *= s_rstd[c]; }
           const int n = a0 + rank * rows_per + 2 * pr;
-          if (n + 1 < p.N) out[(int64_t)(b0 + c) * p.ldc + (n >> 1)] = out_cast<OutT>(silu_mul(g, u));
+          if (n + 1 < p.N) out[(int64_t)(b0 + c) * p.ldc + (n >> 1)] = out_cast<OutT>(gate_mul(g, u, p.act));
         }
       } else {
         for (int i = threadIdx.x; i < cols * rows_mine; i += NTHREADS) {
@@ -605,7 +611,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             OutT* dst = out + (int64_t)t * p.ldc + o0;
             float y[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) y[j] = silu_mul_fast(__uint_as_float(v[h][2 * j]), __uint_as_float(v[h][2 * j + 1]));
+            for (int j = 0; j < 8; ++j)
+              y[j] = p.act == 2 ? gelu_tanh_mul(__uint_as_float(v[h][2 * j]), __uint_as_float(v[h][2 * j + 1]))
+                                : silu_mul_fast(__uint_as_float(v[h][2 * j]), __uint_as_float(v[h][2 * j + 1]));
             if (vec && o0 + 8 <= n_out) {
               uint4 w0;
               __nv_bfloat162* h0 = reinterpret_cast<__nv_bfloat162*>(&w0);
@@ -776,8 +784,8 @@ DINFER_DEFINE_LAST_ERROR()
 // x [tokens, K] (row stride ldx), w [N, K] (row stride ldw), both bf16; out [tokens, N] (row stride ldc)
 // bf16 (out_f32 = 0) or f32.  tokens <= 64: decode orientation with `splits` K splits (at most 8: the
 // CTAs of a tile form a cluster).  More tokens: prompt orientation (two SMs on a tile), splits ignored.
-// act = 1 (N even): the rows of w are (gate, up) pairs and out is [tokens, N / 2],
-// out[t, j] = silu(x w_{2j}) * (x w_{2j+1}).
+// act > 0 (N even): the rows of w are (gate, up) pairs and out is [tokens, N / 2],
+// out[t, j] = g(x w_{2j}) * (x w_{2j+1}) with g = silu (act 1) or the tanh form of gelu (act 2).
 // status: a device int that a kernel sets non-zero when one of its bounded waits ran out.
 //
 // The two halves of an RMSNorm between two decode products (tokens <= 64, see the kernel's header):
@@ -804,7 +812,8 @@ DINFER_API int dinfer_gemm_tc_fused(const void* x, int64_t ldx, const void* w, i
   if (ss_in && (ss_parts <= 0 || ss_stride < tokens))
     return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: the scaled epilogue needs the parts of the sums (parts=%d stride=%d)", ss_parts, ss_stride);
   GemmParams p;
-  p.act = act ? 1 : 0;
+  if (act < 0 || act > 2) return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: unknown gate %d (0 none, 1 silu, 2 tanh-gelu)", act);
+  p.act = act;
   p.resid = resid; p.ldr = ldr; p.norm_w = norm_w; p.norm_w_f32 = norm_w_f32; p.ss_out = ss_out;
   p.ss_in = ss_in; p.ss_parts = ss_parts; p.ss_stride = ss_stride; p.inv_size = inv_size; p.eps = eps;
   p.out = out; p.ldc = ldc; p.tokens = tokens; p.N = N; p.K = K; p.status = status;

@@ -108,13 +108,17 @@ def decode_splits(tokens: int, N: int, K: int) -> int:
     return max(1, min(slots // tiles, k_blocks // 8, MAX_SPLITS))
 
 
+# the gates the product's epilogue knows
+GATES = {False: 0, None: 0, True: 1, "silu": 1, "gelu_tanh": 2}
+
+
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: Optional[int] = None,
-            gated: bool = False, residual: Optional[torch.Tensor] = None, norm_weight: Optional[torch.Tensor] = None,
+            gated=False, residual: Optional[torch.Tensor] = None, norm_weight: Optional[torch.Tensor] = None,
             sums: Optional[torch.Tensor] = None, row_scale=None) -> torch.Tensor:
     """out[tokens, N] = x[tokens, K] @ w[N, K]^T.  out: bfloat16 or float32, last axis contiguous.
 
-    ``gated`` (any number of rows): the rows of w are (gate, up) pairs, out is [tokens, N / 2],
-    out[t, j] = silu(x w_2j) * (x w_2j+1).
+    ``gated`` (any number of rows; True or "silu", or "gelu_tanh"): the rows of w are (gate, up) pairs, out is
+    [tokens, N / 2], out[t, j] = g(x w_2j) * (x w_2j+1) with that g.
     Epilogues of the decode orientation (at most ``DECODE_MAX_TOKENS`` rows):
       ``residual`` [tokens, N] f32 with ``norm_weight`` [N] and ``sums`` [parts, stride >= tokens] f32
         (``parts = residual_parts(...)``): the product is added into the residual, out gets the new
@@ -126,6 +130,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: Optiona
         raise KernelError("gemm_tc: bfloat16 operands with K and row strides multiples of 8 and 16-byte aligned bases")
     tokens, K = x.shape
     N = w.shape[0]
+    if gated not in GATES:
+        raise KernelError(f"gemm_tc: unknown gate {gated!r}")
     if (residual is not None or row_scale is not None) and tokens > DECODE_MAX_TOKENS:
         raise KernelError("gemm_tc: the norm epilogues take at most 64 rows")
     if gated and (N % 2 or residual is not None):
@@ -165,7 +171,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: Optiona
                   c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_float,
                   c_void_p, c_void_p])
     check(lib, f(ptr(x), x.stride(0), ptr(w), w.stride(0), ptr(out), out.stride(0), int(out.dtype == torch.float32),
-                 tokens, N, K, int(splits), int(bool(gated)), r_ptr, ldr, nw_ptr, nw_f32, so_ptr, si_ptr, int(parts),
+                 tokens, N, K, int(splits), GATES[gated], r_ptr, ldr, nw_ptr, nw_f32, so_ptr, si_ptr, int(parts),
                  int(stride), float(inv_size), float(eps), ptr(st["status"]), stream_handle()), "gemm_tc")
     return out
 

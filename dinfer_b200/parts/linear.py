@@ -68,6 +68,8 @@ class Linear:
         One kernel where ``fuses_gate`` (the silu gate), else the product followed by the gate kernel."""
         if activation != "silu":
             act = torch.empty((x.shape[0], self.out_features // 2), dtype=x.dtype, device=x.device)
+            if activation in gemm_ops.GATES and self.fuses_gate(x):
+                return gemm_ops.gemm_tc(x, self.weight, act, gated=activation)
             return ops.gated_act(self(x), act, activation, pairs=True)
         if isinstance(x, HalfNormed):
             act = torch.empty((x.shape[0], self.out_features // 2), dtype=x.xw.dtype, device=x.xw.device)
