@@ -253,17 +253,18 @@ attention_latent_tc_kernel(const LatentTcParams p) {
     if (gr < rows) v = *reinterpret_cast<const uint4*>(p.q + (int64_t)(t0 + gr / p.H) * p.ldq_t + (int64_t)(gr % p.H) * p.ldq_h + c * 8);
     *reinterpret_cast<uint4*>(Qs + (size_t)r * WS + c * 8) = v;
   }
+  // two threads per key: one look at the block table, then the row's 16-byte pieces alternately
   auto load_tile = [&](int kt, int buf) {
-    __nv_bfloat16* dst = Ks + (size_t)buf * TK * WS;
-    for (int i = tid; i < TK * chunks; i += TC_THREADS) {
-      const int key = i / chunks, c = i % chunks;
-      const int j = kt * TK + key;
-      const int page = j < k_end ? table[j / p.block_size] : -1;
-      __nv_bfloat16* d = dst + (size_t)key * WS + c * 8;
-      if (page >= 0) cp_async16(d, p.cache + ((int64_t)page * p.block_size + j % p.block_size) * W + c * 8);
-      else *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
-      if (c == 0) kvalid[buf * TK + key] = page >= 0;
+    const int key = tid >> 1, j = kt * TK + key;
+    const int page = j < k_end ? table[j / p.block_size] : -1;
+    __nv_bfloat16* d = Ks + (size_t)buf * TK * WS + (size_t)key * WS;
+    if (page >= 0) {
+      const __nv_bfloat16* src = p.cache + ((int64_t)page * p.block_size + j % p.block_size) * W;
+      for (int c = tid & 1; c < chunks; c += 2) cp_async16(d + c * 8, src + c * 8);
+    } else {
+      for (int c = tid & 1; c < chunks; c += 2) *reinterpret_cast<uint4*>(d + c * 8) = make_uint4(0, 0, 0, 0);
     }
+    if (!(tid & 1)) kvalid[buf * TK + key] = page >= 0;
     cp_async_commit();
   };
 
@@ -291,6 +292,7 @@ attention_latent_tc_kernel(const LatentTcParams p) {
       for (int n = 0; n < 2; ++n)
 #pragma unroll
         for (int e = 0; e < 4; ++e) s[mt][n][e] = 0.f;
+#pragma unroll 4
     for (int kk = 0; kk < W; kk += 16) {
       uint32_t bfr[4];
       ldsm_x4(bfr, Kt + (size_t)(warp * 16 + (lane & 7) + ((lane >> 4) << 3)) * WS + kk + (((lane >> 3) & 1) << 3));
@@ -412,25 +414,35 @@ attention_latent_tc_kernel(const LatentTcParams p) {
     }
 }
 
-// out[row] = sum_s 2^(m_s - M) part[row, s] / sum_s 2^(m_s - M) l_s, in split order; one warp per (token, head)
+// out[row] = sum_s 2^(m_s - M) part[row, s] / sum_s 2^(m_s - M) l_s, in split order; one block per (token, head)
 __global__ void __launch_bounds__(128)
 attention_latent_fold_kernel(const float* __restrict__ part, const float* __restrict__ ml, __nv_bfloat16* __restrict__ out,
                              int64_t ldo_t, int64_t ldo_h, int rows, int H, int R, int splits) {
+  __shared__ float w_s[64];
+  __shared__ float inv_s;
   pdl_enter();
-  const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (row >= rows) return;
+  const int row = blockIdx.x;
   const float* mlr = ml + (int64_t)row * splits * 2;
-  float M = -INFINITY;
-  for (int s = 0; s < splits; ++s) M = fmaxf(M, mlr[2 * s]);
-  float L = 0.f;
-  for (int s = 0; s < splits; ++s) if (mlr[2 * s] != -INFINITY) L += exp2f(mlr[2 * s] - M) * mlr[2 * s + 1];
-  const float inv = L > 0.f ? 1.f / L : 0.f;
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float M = -INFINITY;
+    for (int s = lane; s < splits; s += 32) M = fmaxf(M, mlr[2 * s]);
+    M = warp_max(M);
+    for (int s = lane; s < splits; s += 32) w_s[s] = mlr[2 * s] == -INFINITY ? 0.f : exp2f(mlr[2 * s] - M);
+    __syncwarp();
+    if (lane == 0) {
+      float L = 0.f;
+      for (int s = 0; s < splits; ++s) L += w_s[s] * mlr[2 * s + 1];
+      inv_s = L > 0.f ? 1.f / L : 0.f;
+    }
+  }
+  __syncthreads();
   __nv_bfloat16* dst = out + (int64_t)(row / H) * ldo_t + (int64_t)(row % H) * ldo_h;
-  for (int c = lane; c < R; c += 32) {
+  const float* pr = part + (int64_t)row * splits * R;
+  for (int c = threadIdx.x; c < R; c += blockDim.x) {
     float a = 0.f;
-    for (int s = 0; s < splits; ++s)
-      if (mlr[2 * s] != -INFINITY) a += exp2f(mlr[2 * s] - M) * part[((int64_t)row * splits + s) * R + c];
-    dst[c] = __float2bfloat16_rn(a * inv);
+    for (int s = 0; s < splits; ++s) a += w_s[s] * pr[(int64_t)s * R + c];
+    dst[c] = __float2bfloat16_rn(a * inv_s);
   }
 }
 
@@ -477,7 +489,7 @@ DINFER_API int dinfer_attention_latent_tc(const void* q, int64_t ldq_t, int64_t 
       (reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(cache) & 15) || (reinterpret_cast<uintptr_t>(out) & 3))
     return refuse(DINFER_BAD_ARGUMENT, "attention_latent_tc: R and P in multiples of 16, R <= 512, 16-byte aligned rows (R=%d P=%d)", R, P);
   if (splits > 1 && (!part || !ml)) return refuse(DINFER_BAD_ARGUMENT, "attention_latent_tc: splits without scratch");
-  if (splits > 65535) return refuse(DINFER_BAD_ARGUMENT, "attention_latent_tc: too many splits");
+  if (splits > 64) return refuse(DINFER_BAD_ARGUMENT, "attention_latent_tc: at most 64 splits");
   if (T == 0 || row_tiles == 0) return 0;
   LatentTcParams p;
   p.q = (const __nv_bfloat16*)q; p.ldq_t = ldq_t; p.ldq_h = ldq_h;
@@ -495,7 +507,7 @@ DINFER_API int dinfer_attention_latent_tc(const void* q, int64_t ldq_t, int64_t 
   else { if (nt <= 1) GO(4, 1); else if (nt <= 2) GO(4, 2); else GO(4, 4); }
 #undef GO
   if (rc != 0 || splits == 1) return rc;
-  launch_pdl(attention_latent_fold_kernel, dim3((T * H + 3) / 4), dim3(128), 0, stream, (const float*)part, (const float*)ml,
+  launch_pdl(attention_latent_fold_kernel, dim3(T * H), dim3(128), 0, stream, (const float*)part, (const float*)ml,
              (__nv_bfloat16*)out, ldo_t, ldo_h, T * H, H, R, splits);
   return cuda_status("attention_latent_fold");
 }

@@ -1,8 +1,9 @@
 // A routed feed-forward (mixture of experts), as five kernels that never meet the host between them:
 //
-//   moe_router     per token: 32-bit router logits z = W_r h, scores (softmax over all experts, or a sigmoid each),
-//                  the `top` largest scores (ties to the lower index) -> expert ids and weights (the scores, or
-//                  the scores divided by their sum); optionally the gate of a shared expert, sigmoid(w_g . h)
+//   moe_route      per token, from the 32-bit router logits z = W_r h (a product of its own, f32 out): scores (softmax
+//                  over all experts, or a sigmoid each), the `top` largest scores (ties to the lower index) -> expert
+//                  ids and weights (the scores, or the scores divided by their sum); optionally the gate of a shared
+//                  expert, the sigmoid of the logit in the column behind the experts' 
 //   moe_align      the (token, choice) pairs counted per expert and laid out expert by expert, each expert's run
 //                  padded to a multiple of the row tile, so that a row tile belongs to one expert
 //   moe_gemm       grouped product over those tiles: rows gathered by pair (first product, an activation in the
@@ -33,31 +34,18 @@ __device__ __forceinline__ float activate(float z, int act) {
 // ---------------------------------------------------------------- router
 constexpr int RW = 4;   // warps (tokens) per block
 
-template <typename TA, typename TW>
 __global__ void __launch_bounds__(RW * 32)
-moe_router_kernel(const TA* __restrict__ h, int64_t ldh, const TW* __restrict__ wr, const TW* __restrict__ wg,
-                  int* __restrict__ ids, float* __restrict__ weights, float* __restrict__ gate, int T, int K, int E,
-                  int top, int sigmoid_scores, int renorm) {
+moe_route_kernel(const float* __restrict__ logits, int64_t ldz, int* __restrict__ ids, float* __restrict__ weights,
+                 float* __restrict__ gate, int T, int E, int top, int sigmoid_scores, int renorm) {
   extern __shared__ float sm[];                          // RW * E scores
   pdl_enter();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * RW + warp;
   if (t >= T) return;
   float* z = sm + warp * E;
-  const TA* x = h + (int64_t)t * ldh;
-  for (int e = 0; e < E; ++e) {
-    const TW* w = wr + (int64_t)e * K;
-    float a = 0.f;
-    for (int k = lane; k < K; k += 32) a = fmaf(to_f32<TA>(x[k]), to_f32<TW>(w[k]), a);
-    a = warp_sum(a);
-    if (lane == 0) z[e] = a;
-  }
-  if (wg && gate) {
-    float a = 0.f;
-    for (int k = lane; k < K; k += 32) a = fmaf(to_f32<TA>(x[k]), to_f32<TW>(wg[k]), a);
-    a = warp_sum(a);
-    if (lane == 0) gate[t] = 1.f / (1.f + expf(-a));
-  }
+  const float* row = logits + (int64_t)t * ldz;
+  for (int e = lane; e < E; e += 32) z[e] = row[e];
+  if (gate && lane == 0) gate[t] = 1.f / (1.f + expf(-row[E]));      // the column behind the experts' is the gate's
   __syncwarp();
   if (sigmoid_scores) {
     for (int e = lane; e < E; e += 32) z[e] = 1.f / (1.f + expf(-z[e]));
@@ -353,22 +341,17 @@ __global__ void activation_kernel(const TA* __restrict__ x, TA* __restrict__ out
 
 DINFER_DEFINE_LAST_ERROR()
 
-// h [T, K] rows of stride ldh; wr [E, K], wg [K] or null (w_dtype); ids, weights [T, top]; gate [T] or null.
-DINFER_API int dinfer_moe_router(const void* h, int64_t ldh, const void* wr, const void* wg, int* ids, float* weights,
-                                 float* gate, int T, int K, int E, int top, int sigmoid_scores, int renorm,
-                                 int act_dtype, int w_dtype, cudaStream_t stream) {
-  if (T < 0 || K <= 0 || E <= 0 || top <= 0 || top > E || ldh < K)
-    return refuse(DINFER_BAD_ARGUMENT, "moe_router: bad sizes T=%d K=%d E=%d top=%d", T, K, E, top);
-  if ((size_t)RW * E * sizeof(float) > 48 * 1024) return refuse(DINFER_BAD_ARGUMENT, "moe_router: %d experts above the limit %d", E, 48 * 1024 / 4 / RW);
+// logits [T, >= E (+ 1)] f32 rows of stride ldz (column E: the shared expert's gate logit, read when gate is given);
+// ids, weights [T, top]; gate [T] or null.
+DINFER_API int dinfer_moe_route(const float* logits, int64_t ldz, int* ids, float* weights, float* gate, int T, int E,
+                                int top, int sigmoid_scores, int renorm, cudaStream_t stream) {
+  if (T < 0 || E <= 0 || top <= 0 || top > E || ldz < E + (gate ? 1 : 0))
+    return refuse(DINFER_BAD_ARGUMENT, "moe_route: bad sizes T=%d E=%d top=%d ldz=%lld", T, E, top, (long long)ldz);
+  if ((size_t)RW * E * sizeof(float) > 48 * 1024) return refuse(DINFER_BAD_ARGUMENT, "moe_route: %d experts above the limit %d", E, 48 * 1024 / 4 / RW);
   if (T == 0) return 0;
-  DINFER_DISPATCH_DTYPE(act_dtype, TA,
-    DINFER_DISPATCH_DTYPE(w_dtype, TW, {
-      launch_pdl(moe_router_kernel<TA, TW>, dim3((T + RW - 1) / RW), dim3(RW * 32), (size_t)RW * E * sizeof(float),
-                 stream, (const TA*)h, ldh, (const TW*)wr, (const TW*)wg, ids, weights, gate, T, K, E, top,
-                 sigmoid_scores, renorm);
-      return cuda_status("moe_router");
-    }));
-  return 0;
+  launch_pdl(moe_route_kernel, dim3((T + RW - 1) / RW), dim3(RW * 32), (size_t)RW * E * sizeof(float), stream, logits, ldz,
+             ids, weights, gate, T, E, top, sigmoid_scores, renorm);
+  return cuda_status("moe_route");
 }
 
 // ids [pairs]; sorted [cap], cap >= pairs + E * (BM - 1) rounded up to BM; tile_expert [cap / BM].

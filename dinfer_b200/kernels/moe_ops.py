@@ -12,31 +12,37 @@ from .ops import _fn, _rows_contiguous
 ACTIVATIONS = {"none": 0, "relu2": 1, "silu": 2, "gelu_tanh": 3, "relu": 4}
 
 
+def route(logits: torch.Tensor, num_experts: int, top_k: int, scoring: str = "softmax", renormalize: bool = False,
+          has_gate: bool = False) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
+    """From 32-bit router logits [T, E (+ 1)]: (expert ids int32 [T, top_k], weights f32 [T, top_k], gate f32 [T] or
+    None).  ``scoring`` softmax (over all experts) or sigmoid; the weights are the chosen scores, divided by their sum
+    with ``renormalize``; ``has_gate``: column E holds a shared expert's gate logit, gate = its sigmoid."""
+    require_cuda(logits)
+    _rows_contiguous(logits, "moe route")
+    T = logits.shape[0]
+    if scoring not in ("softmax", "sigmoid"):
+        raise KernelError(f"moe route: unknown scoring {scoring!r}")
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.shape[1] != num_experts + int(has_gate):
+        raise KernelError("moe route: logits f32 [T, E (+ 1)]")
+    ids = torch.empty((T, top_k), dtype=torch.int32, device=logits.device)
+    weights = torch.empty((T, top_k), dtype=torch.float32, device=logits.device)
+    gate = torch.empty((T,), dtype=torch.float32, device=logits.device) if has_gate else None
+    lib, f = _fn("moe", "dinfer_moe_route",
+                 [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    check(lib, f(ptr(logits), logits.stride(0), ptr(ids), ptr(weights), ptr(gate), T, num_experts, top_k,
+                 int(scoring == "sigmoid"), int(bool(renormalize)), stream_handle()), "moe_route")
+    return ids, weights, gate
+
+
 def router(h: torch.Tensor, w_router: torch.Tensor, top_k: int, scoring: str = "softmax", renormalize: bool = False,
            w_gate: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
-    """32-bit router: (expert ids int32 [T, top_k], weights f32 [T, top_k], gate f32 [T] or None).  ``scoring``
-    softmax (over all experts) or sigmoid; the weights are the chosen scores, divided by their sum with
-    ``renormalize``; ``w_gate`` [1, K]: gate[t] = sigmoid(w_gate . h[t])."""
-    require_cuda(h, w_router, w_gate)
-    _rows_contiguous(h, "moe router")
-    T, K = h.shape
-    E = w_router.shape[0]
-    if scoring not in ("softmax", "sigmoid"):
-        raise KernelError(f"moe router: unknown scoring {scoring!r}")
-    if w_router.shape[1] != K or not w_router.is_contiguous():
-        raise KernelError("moe router: weight [E, K] contiguous")
-    if w_gate is not None and (w_gate.numel() != K or w_gate.dtype != w_router.dtype or not w_gate.is_contiguous()):
-        raise KernelError("moe router: gate weight [K] of the router's dtype")
-    ids = torch.empty((T, top_k), dtype=torch.int32, device=h.device)
-    weights = torch.empty((T, top_k), dtype=torch.float32, device=h.device)
-    gate = torch.empty((T,), dtype=torch.float32, device=h.device) if w_gate is not None else None
-    lib, f = _fn("moe", "dinfer_moe_router",
-                 [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                  c_int, c_int, c_int, c_void_p])
-    check(lib, f(ptr(h), h.stride(0), ptr(w_router), ptr(w_gate), ptr(ids), ptr(weights), ptr(gate), T, K, E, top_k,
-                 int(scoring == "sigmoid"), int(bool(renormalize)), dtype_code(h.dtype), dtype_code(w_router.dtype),
-                 stream_handle()), "moe_router")
-    return ids, weights, gate
+    """The router from its input: logits by the 32-bit product (``w_router`` [E, K], and ``w_gate`` [K] as one more
+    row), then ``route``."""
+    from .ops import gemm_f32
+    w = w_router if w_gate is None else torch.cat([w_router, w_gate.reshape(1, -1).to(w_router.dtype)])
+    z = torch.empty((h.shape[0], w.shape[0]), dtype=torch.float32, device=h.device)
+    gemm_f32(h, w.contiguous(), z)
+    return route(z, w_router.shape[0], top_k, scoring, renormalize, w_gate is not None)
 
 
 def row_tile(pairs: int, num_experts: int) -> int:

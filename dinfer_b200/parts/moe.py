@@ -3,7 +3,8 @@ outputs are summed with the router's weights, and an optional shared expert runs
 
 Data flow of one step (nothing goes through the host; every size is fixed by the number of tokens, so the step
 can be captured in a CUDA graph):
-  ids, w, g = router(x)                 f32 logits -> scores -> top-k (+ the shared expert's gate)
+  z = x [W_r; w_g]^T                    f32 logits of the router (and of the shared expert's gate) by the engine's product
+  ids, w, g = route(z)                  scores -> top-k (+ the gate's sigmoid)
   layout    = align(ids)                (token, choice) pairs expert by expert, runs padded to the row tile
   u         = act(x[pair] W_up[e]^T)    grouped product, rows gathered
   y[pair]   = (u W_down[e]^T) * w[pair] grouped product, rows scattered back
@@ -52,7 +53,8 @@ class MoE(FeedForward):
         self.names = {"router": n("router", "router.weight"), "up": n("expert_up", "experts.{e}.up.weight"),
                       "down": n("expert_down", "experts.{e}.down.weight"), "s_up": n("shared_up", "shared.up.weight"),
                       "s_down": n("shared_down", "shared.down.weight"), "s_gate": n("shared_gate_proj", "shared.gate.weight")}
-        self.router_w = self.gate_w = self.w_up = self.w_down = None
+        self.router: Optional[Linear] = None
+        self.w_up = self.w_down = None
         self.shared_up: Optional[Linear] = None
         self.shared_down: Optional[Linear] = None
 
@@ -69,7 +71,10 @@ class MoE(FeedForward):
         return d
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.router_w = tensors[self.names["router"]].contiguous()
+        router_w = tensors[self.names["router"]]
+        if self.shared_ff and self.shared_gate:             # the gate's row rides behind the experts' rows
+            router_w = torch.cat([router_w, tensors[self.names["s_gate"]].to(router_w.dtype).reshape(1, -1)])
+        self.router = Linear(router_w)
         ups = [tensors[self.names["up"].format(e=e)] for e in range(self.E)]
         downs = [tensors[self.names["down"].format(e=e)] for e in range(self.E)]
         dt = torch.float32 if any(t.dtype == torch.float32 for t in ups + downs) else ups[0].dtype
@@ -78,18 +83,19 @@ class MoE(FeedForward):
         if self.shared_ff:
             self.shared_up = Linear(tensors[self.names["s_up"]])
             self.shared_down = Linear(tensors[self.names["s_down"]])
-            if self.shared_gate:
-                self.gate_w = tensors[self.names["s_gate"]].to(self.router_w.dtype).reshape(-1).contiguous()
 
     def kernel_libraries(self):
-        libs = ["moe"]
+        libs = ["moe"] + self.router.kernel_libraries()
         if self.shared_ff:
             libs += self.shared_up.kernel_libraries() + self.shared_down.kernel_libraries()
         return libs
 
     def forward(self, x, ctx=None, sink=None):
         T = x.shape[0]
-        ids, weights, gate = moe_ops.router(x, self.router_w, self.top, self.scoring, self.renormalize, self.gate_w)
+        # 32-bit logits: products of the stored values summed in 32-bit (the same product that makes the model's logits)
+        z = self.router(x, out_dtype=torch.float32)
+        ids, weights, gate = moe_ops.route(z, self.E, self.top, self.scoring, self.renormalize,
+                                           bool(self.shared_ff and self.shared_gate))
         pairs = T * self.top
         tile = moe_ops.row_tile(pairs, self.E)
         order, tile_expert = moe_ops.align(ids, self.E, tile)
