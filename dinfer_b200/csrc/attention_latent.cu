@@ -151,24 +151,28 @@ DINFER_API int dinfer_attention_latent_generic(const void* q, int64_t ldq_t, int
 // ================================================================ tensor cores (bfloat16)
 // The same attention on mma.sync m16n8k16 with 32-bit accumulation, for prompt portions and decoded tokens alike.
 // Since every head scores against the same rows, the (token, head) pairs of a request are the rows of the problem:
-// a CTA of four warps owns BM = 16 * MT of them (a decoded token: its H heads) and walks the request's cached rows
+// a CTA of eight warps owns BM = 16 * MT of them (a decoded token: its H heads) and walks the request's cached rows
 // in tiles of 64 keys, fetched page by page with cp.async into a double buffer [64][R + P] that serves as K and,
 // in its first R columns, as V:
-//   S = Q K^T      each warp 16 keys of the tile, all row tiles           -> shared memory (f32)
-//   softmax        128 / BM threads per row, online maximum and sum (exp2f), P as bf16 -> shared memory
-//   O += P V       each warp ceil(R / 32) columns (NT n-tiles), all row tiles, V read with ldmatrix.trans
+//   S = Q K^T      each warp 8 keys of the tile, all row tiles            -> shared memory (f32)
+//   softmax        256 / BM threads per row, online maximum and sum (exp2f), P as bf16 -> shared memory
+//   O += P V       each warp ceil(R / 64) n-tiles of 8 columns (NT), all row tiles, V read with ldmatrix.trans
 // With `splits` > 1 the key tiles of a row tile are shared among that many CTAs (grid.y); each leaves its
 // unnormalised sums, maximum and sum in scratch and a second kernel folds them, in split order.
 namespace {
 
 constexpr int TK = 64;           // keys per tile
-constexpr int TC_THREADS = 128;
+constexpr int TC_WARPS = 8;
+constexpr int TC_THREADS = 32 * TC_WARPS;
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x2(uint32_t (&r)[2], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(smem_u32(p)));
 }
 __device__ __forceinline__ void ldsm_x2_trans(uint32_t (&r)[2], const void* p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(smem_u32(p)));
@@ -253,18 +257,19 @@ attention_latent_tc_kernel(const LatentTcParams p) {
     if (gr < rows) v = *reinterpret_cast<const uint4*>(p.q + (int64_t)(t0 + gr / p.H) * p.ldq_t + (int64_t)(gr % p.H) * p.ldq_h + c * 8);
     *reinterpret_cast<uint4*>(Qs + (size_t)r * WS + c * 8) = v;
   }
-  // two threads per key: one look at the block table, then the row's 16-byte pieces alternately
+  // TPK threads per key: one look at the block table, then the row's 16-byte pieces in turn
+  constexpr int TPK = TC_THREADS / TK;
   auto load_tile = [&](int kt, int buf) {
-    const int key = tid >> 1, j = kt * TK + key;
+    const int key = tid / TPK, j = kt * TK + key;
     const int page = j < k_end ? table[j / p.block_size] : -1;
     __nv_bfloat16* d = Ks + (size_t)buf * TK * WS + (size_t)key * WS;
     if (page >= 0) {
       const __nv_bfloat16* src = p.cache + ((int64_t)page * p.block_size + j % p.block_size) * W;
-      for (int c = tid & 1; c < chunks; c += 2) cp_async16(d + c * 8, src + c * 8);
+      for (int c = tid % TPK; c < chunks; c += TPK) cp_async16(d + c * 8, src + c * 8);
     } else {
-      for (int c = tid & 1; c < chunks; c += 2) *reinterpret_cast<uint4*>(d + c * 8) = make_uint4(0, 0, 0, 0);
+      for (int c = tid % TPK; c < chunks; c += TPK) *reinterpret_cast<uint4*>(d + c * 8) = make_uint4(0, 0, 0, 0);
     }
-    if (!(tid & 1)) kvalid[buf * TK + key] = page >= 0;
+    if (tid % TPK == 0) kvalid[buf * TK + key] = page >= 0;
     cp_async_commit();
   };
 
@@ -284,35 +289,30 @@ attention_latent_tc_kernel(const LatentTcParams p) {
     if (kt + 1 < kt1) load_tile(kt + 1, buf ^ 1);
     const __nv_bfloat16* Kt = Ks + (size_t)buf * TK * WS;
 
-    // ---- S = Q K^T: this warp's 16 keys
-    float s[MT][2][4];
+    // ---- S = Q K^T: this warp's 8 keys (one n-tile)
+    float s[MT][4];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-      for (int n = 0; n < 2; ++n)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) s[mt][n][e] = 0.f;
+      for (int e = 0; e < 4; ++e) s[mt][e] = 0.f;
 #pragma unroll 4
     for (int kk = 0; kk < W; kk += 16) {
-      uint32_t bfr[4];
-      ldsm_x4(bfr, Kt + (size_t)(warp * 16 + (lane & 7) + ((lane >> 4) << 3)) * WS + kk + (((lane >> 3) & 1) << 3));
+      uint32_t bfr[2];
+      ldsm_x2(bfr, Kt + (size_t)(warp * 8 + (lane & 7)) * WS + kk + (((lane >> 3) & 1) << 3));
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
         uint32_t afr[4];
         ldsm_x4(afr, Qs + (size_t)(mt * 16 + (lane & 15)) * WS + kk + ((lane >> 4) << 3));
-        mma_bf16(s[mt][0], afr, bfr[0], bfr[1]);
-        mma_bf16(s[mt][1], afr, bfr[2], bfr[3]);
+        mma_bf16(s[mt], afr, bfr[0], bfr[1]);
       }
     }
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-      for (int n = 0; n < 2; ++n) {
-        const int col = warp * 16 + n * 8 + 2 * (lane & 3);
-        const int row = mt * 16 + (lane >> 2);
-        *reinterpret_cast<float2*>(Ss + row * (TK + 4) + col) = make_float2(s[mt][n][0] * p.scale_log2, s[mt][n][1] * p.scale_log2);
-        *reinterpret_cast<float2*>(Ss + (row + 8) * (TK + 4) + col) = make_float2(s[mt][n][2] * p.scale_log2, s[mt][n][3] * p.scale_log2);
-      }
+    for (int mt = 0; mt < MT; ++mt) {
+      const int col = warp * 8 + 2 * (lane & 3);
+      const int row = mt * 16 + (lane >> 2);
+      *reinterpret_cast<float2*>(Ss + row * (TK + 4) + col) = make_float2(s[mt][0] * p.scale_log2, s[mt][1] * p.scale_log2);
+      *reinterpret_cast<float2*>(Ss + (row + 8) * (TK + 4) + col) = make_float2(s[mt][2] * p.scale_log2, s[mt][3] * p.scale_log2);
+    }
     __syncthreads();
 
     // ---- softmax of the tile: TPR threads per row, KPT keys each
@@ -468,10 +468,8 @@ int launch_tc(const LatentTcParams& p, int row_tiles, cudaStream_t stream) {
 
 // Most row tiles per SM-wide grid the caller should assume: BM rows per tile for these sizes.
 DINFER_API int dinfer_attention_latent_tc_rows(int R, int max_rows_per_req) {
-  const int nt = (R + 31) / 32;
   if (max_rows_per_req <= 16) return 16;
-  if (nt > 8) return max_rows_per_req <= 16 ? 16 : 32;
-  if (nt > 4) return 32;
+  if (R > 256) return 32;                                    // a wider latent leaves shared memory for 32 query rows
   return max_rows_per_req <= 32 ? 32 : 64;
 }
 
@@ -499,11 +497,11 @@ DINFER_API int dinfer_attention_latent_tc(const void* q, int64_t ldq_t, int64_t 
   p.block_size = block_size; p.window = window; p.splits = splits; p.scale_log2 = scale * LOG2E;
   p.part = part; p.ml = ml;
   const int bm = dinfer_attention_latent_tc_rows(R, max_rows_per_req);
-  const int nt = (R + 31) / 32;
+  const int nt = (R + 8 * TC_WARPS - 1) / (8 * TC_WARPS);      // n-tiles of the output a warp owns
   int rc;
 #define GO(MT, NT) rc = launch_tc<MT, NT>(p, row_tiles, stream)
-  if (bm == 16) { if (nt <= 1) GO(1, 1); else if (nt <= 2) GO(1, 2); else if (nt <= 4) GO(1, 4); else if (nt <= 8) GO(1, 8); else GO(1, 16); }
-  else if (bm == 32) { if (nt <= 1) GO(2, 1); else if (nt <= 2) GO(2, 2); else if (nt <= 4) GO(2, 4); else if (nt <= 8) GO(2, 8); else GO(2, 16); }
+  if (bm == 16) { if (nt <= 1) GO(1, 1); else if (nt <= 2) GO(1, 2); else if (nt <= 4) GO(1, 4); else GO(1, 8); }
+  else if (bm == 32) { if (nt <= 1) GO(2, 1); else if (nt <= 2) GO(2, 2); else if (nt <= 4) GO(2, 4); else GO(2, 8); }
   else { if (nt <= 1) GO(4, 1); else if (nt <= 2) GO(4, 2); else GO(4, 4); }
 #undef GO
   if (rc != 0 || splits == 1) return rc;

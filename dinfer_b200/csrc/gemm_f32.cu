@@ -92,10 +92,68 @@ gemm_rows_kernel(const TA* __restrict__ A, int64_t lda, const TW* __restrict__ W
   }
 }
 
+// The same for bfloat16 operands whose rows are 16-byte aligned (K a multiple of 8): every lane takes eight
+// consecutive k at once (one 16-byte load of the weight row and one of each A row), four output columns per block,
+// so a small K still fills the machine with loads in flight.  Products and sums are 32-bit.
+template <typename TC, int ROWS>
+__global__ void __launch_bounds__(128)
+gemm_rows_bf16x8_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, const __nv_bfloat16* __restrict__ W, int64_t ldw,
+                        TC* __restrict__ C, int64_t ldc, int M, int N, int K, int64_t sa, int64_t sw, int64_t sc) {
+  A += (int64_t)blockIdx.z * sa; W += (int64_t)blockIdx.z * sw; C += (int64_t)blockIdx.z * sc;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * 4 + warp;
+  if (n >= N) return;
+  const __nv_bfloat16* w = W + (int64_t)n * ldw;
+  float acc[ROWS];
+#pragma unroll
+  for (int m = 0; m < ROWS; ++m) acc[m] = 0.f;
+  for (int k = lane * 8; k < K; k += 256) {
+    const uint4 wv = *reinterpret_cast<const uint4*>(w + k);
+    const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv);
+    float wf[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(wp[j]); wf[2 * j] = f.x; wf[2 * j + 1] = f.y; }
+#pragma unroll
+    for (int m = 0; m < ROWS; ++m) {
+      if (m < M) {
+        const uint4 av = *reinterpret_cast<const uint4*>(A + (int64_t)m * lda + k);
+        const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&av);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(ap[j]);
+          acc[m] = fmaf(f.x, wf[2 * j], acc[m]);
+          acc[m] = fmaf(f.y, wf[2 * j + 1], acc[m]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < ROWS; ++m) {
+    const float s = warp_sum(acc[m]);
+    if (lane == 0 && m < M) C[(int64_t)m * ldc + n] = from_f32<TC>(s);
+  }
+}
+
+template <typename TA, typename TW> struct both_bf16 { static constexpr bool value = false; };
+template <> struct both_bf16<__nv_bfloat16, __nv_bfloat16> { static constexpr bool value = true; };
+
 template <typename TA, typename TW, typename TC>
 int launch(const void* A, int64_t lda, const void* W, int64_t ldw, void* C, int64_t ldc, int M, int N,
            int K, cudaStream_t stream, int batch = 1, int64_t sa = 0, int64_t sw = 0, int64_t sc = 0) {
   if (batch > 65535) return refuse(DINFER_BAD_ARGUMENT, "gemm_f32: batch=%d too large", batch);
+  if constexpr (both_bf16<TA, TW>::value) {
+    const auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    if (M <= 32 && (M <= 8 || batch > 1) && K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 && sa % 8 == 0 && sw % 8 == 0 &&
+        al(A) && al(W)) {
+      const dim3 grid((N + 3) / 4, 1, batch);
+      const auto* a = (const __nv_bfloat16*)A;
+      const auto* w = (const __nv_bfloat16*)W;
+      if (M <= 8) gemm_rows_bf16x8_kernel<TC, 8><<<grid, 128, 0, stream>>>(a, lda, w, ldw, (TC*)C, ldc, M, N, K, sa, sw, sc);
+      else if (M <= 16) gemm_rows_bf16x8_kernel<TC, 16><<<grid, 128, 0, stream>>>(a, lda, w, ldw, (TC*)C, ldc, M, N, K, sa, sw, sc);
+      else gemm_rows_bf16x8_kernel<TC, 32><<<grid, 128, 0, stream>>>(a, lda, w, ldw, (TC*)C, ldc, M, N, K, sa, sw, sc);
+      return cuda_status("gemm_f32");
+    }
+  }
   if (M <= 8) {
     gemm_rows_kernel<TA, TW, TC, 8><<<dim3((N + 7) / 8, 1, batch), 256, 0, stream>>>(
         (const TA*)A, lda, (const TW*)W, ldw, (TC*)C, ldc, M, N, K, sa, sw, sc);
