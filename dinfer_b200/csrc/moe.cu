@@ -202,9 +202,10 @@ moe_gemm_simt_kernel(const TA* __restrict__ A, int64_t lda, const TW* __restrict
 }
 
 // ---------------------------------------------------------------- grouped product on tensor cores (bfloat16)
-// The same tiles on mma.sync m16n8k16 with 32-bit accumulation: 4 warps, tile BM x 64, K in steps of 32 through a
+// The same tiles on mma.sync m16n8k16 with 32-bit accumulation: 4 warps, K in steps of 32 through a
 // double buffer filled with cp.async (A rows gathered by pair, the expert's weight rows as they lie).  BM = 64:
-// warps 2 x 2, each 32 x 32; BM = 16 (decode steps: an expert gets a row or two): each warp 16 columns.
+// tile 64 x 128, warps 2 x 2, each 32 x 64; BM = 16 (decode steps: an expert gets a row or two): tile 16 x 64, each
+// warp 16 columns.
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -227,7 +228,7 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, const __nv
                     __nv_bfloat16* __restrict__ C, int64_t ldc, const int* __restrict__ sorted,
                     const int* __restrict__ tile_expert, const float* __restrict__ weights, int pairs, int top, int N,
                     int K, int act) {
-  constexpr int BN = 64, BK = 32, LD = BK + 8;
+  constexpr int BN = BM == 64 ? 128 : 64, BK = 32, LD = BK + 8;
   constexpr int WM = BM == 64 ? 2 : 1, WN = 4 / WM;          // warps along rows and columns
   constexpr int MTW = BM / (16 * WM), NTW = BN / (8 * WN);   // m16 and n8 tiles per warp
   __shared__ __align__(16) __nv_bfloat16 As[2][BM][LD];
@@ -378,6 +379,7 @@ DINFER_API int dinfer_moe_gemm(const void* A, int64_t lda, const void* W, void* 
   if (grid.y > 65535) return refuse(DINFER_BAD_ARGUMENT, "moe_gemm: too many row tiles (%d)", (int)grid.y);
   if (act_dtype == DINFER_BF16 && w_dtype == DINFER_BF16 && K % 8 == 0 && lda % 8 == 0 &&
       !(reinterpret_cast<uintptr_t>(A) & 15) && !(reinterpret_cast<uintptr_t>(W) & 15)) {
+    if (BM == 64) grid.x = (N + 127) / 128;
 #define GO_MMA(BM_, MODE_)                                                                                         \
   launch_pdl(moe_gemm_mma_kernel<BM_, MODE_>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)A, lda,           \
              (const __nv_bfloat16*)W, (__nv_bfloat16*)C, ldc, sorted, tile_expert, weights, pairs, top, N, K, act)
