@@ -60,6 +60,14 @@ struct GemmParams {
   int ss_stride;                 // floats between the parts of ss_out / ss_in
   float inv_size, eps;
   int* status;                   // device status word: 0 = fine
+  // grouped mode (prompt orientation): the 256-row tile m of x belongs to expert tile_expert[m] (-1: no rows, the tile
+  // is skipped), whose N weight rows start at row tile_expert[m] * N of w.  grp_epi 0: out rows as they lie, grp_act
+  // applied (1 relu squared, 2 silu, 3 tanh-gelu, 4 relu); 1: row t goes to out row sorted[t] times row_w[sorted[t]]
+  // (sorted[t] >= pairs: a padding row, not written)
+  const int* tile_expert = nullptr;
+  const int* sorted = nullptr;
+  const float* row_w = nullptr;
+  int pairs = 0, grp_epi = 0, grp_act = 0;
 };
 
 // ---- PTX wrappers
@@ -158,6 +166,15 @@ __device__ __forceinline__ float gelu_tanh_mul(float g, float u) {
   return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
 }
 __device__ __forceinline__ float gate_mul(float g, float u, int act) { return act == 2 ? gelu_tanh_mul(g, u) : silu_mul(g, u); }
+__device__ __forceinline__ float grouped_act(float z, int act) {
+  switch (act) {
+    case 1: { const float r = fmaxf(z, 0.f); return r * r; }
+    case 2: return z / (1.f + expf(-z));
+    case 3: return gelu_tanh_mul(z, 1.f);
+    case 4: return fmaxf(z, 0.f);
+    default: return z;
+  }
+}
 
 template <int N_TILE> constexpr int tmem_cols() { return N_TILE <= 32 ? 32 : (N_TILE <= 64 ? 64 : (N_TILE <= 128 ? 128 : 256)); }
 // Rows of the tile that one CTA of a split-K cluster owns, and the floats of its receive buffer
@@ -537,7 +554,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       uint32_t it = 0;
       bool ok = true;
       for (int tile = pair; tile < tiles && ok; tile += pairs) {
-        const int m0 = (tile % m_tiles) * 256 + (int)rank * 128, n0 = (tile / m_tiles) * NT + (int)rank * (NT / 2);
+        int expert = 0;
+        if (p.tile_expert) { expert = p.tile_expert[tile % m_tiles]; if (expert < 0) continue; }
+        const int m0 = (tile % m_tiles) * 256 + (int)rank * 128;
+        const int n0 = expert * p.N + (tile / m_tiles) * NT + (int)rank * (NT / 2);
         for (int kb = 0; kb < total_kb; ++kb, ++it) {
           const uint32_t s = it % C_STAGES;
           if (!mbar_wait(smem_u32(&empty_bar[s]), ((it / C_STAGES) & 1) ^ 1)) { s_abort = 1; atomicExch(p.status, 1); ok = false; break; }
@@ -555,6 +575,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       uint32_t it = 0, lt = 0;
       bool ok = true;
       for (int tile = pair; tile < tiles && ok; tile += pairs, ++lt) {
+        if (p.tile_expert && p.tile_expert[tile % m_tiles] < 0) { --lt; continue; }       // a tile without rows
         const uint32_t b = lt % C_ACC_BUFS;
         if (!mbar_wait_cluster(smem_u32(&acc_empty_bar[b]), ((lt / C_ACC_BUFS) & 1) ^ 1)) { s_abort = 1; atomicExch(p.status, 2); break; }
         tcgen05_fence_after();
@@ -581,6 +602,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int n_out = GATED ? p.N / 2 : p.N;
     uint32_t lt = 0;
     for (int tile = pair; tile < tiles; tile += pairs, ++lt) {
+      if (p.tile_expert && p.tile_expert[tile % m_tiles] < 0) { --lt; continue; }         // a tile without rows
       const uint32_t b = lt % C_ACC_BUFS;
       const int m0 = (tile % m_tiles) * 256 + (int)rank * 128, n0 = (tile / m_tiles) * NT;
       if (total_kb > 0) {
@@ -591,6 +613,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         tcgen05_fence_after();
       }
       const int t = m0 + r;
+      int64_t t_out = t;                                        // the output row of this thread's accumulator row
+      float row_scale = 1.f;
+      bool skip_row = false;
+      if (p.tile_expert && p.grp_epi == 1 && t < p.tokens) {
+        const int pr = p.sorted[t];
+        skip_row = pr >= p.pairs;
+        if (!skip_row) { t_out = pr; row_scale = p.row_w[pr]; }
+      }
       const uint32_t acc = tmem + ((uint32_t)(quarter * 32) << 16) + b * NT;
 #pragma unroll 1
       for (int c0 = 0; c0 < NT; c0 += 32) {
@@ -603,7 +633,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
           for (int j = 0; j < 16; ++j) { v[0][j] = 0u; v[1][j] = 0u; }
         }
-        if (t >= p.tokens) continue;
+        if (t >= p.tokens || skip_row) continue;
+        if (p.tile_expert) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float x = __uint_as_float(v[h][j]);
+              v[h][j] = __float_as_uint(p.grp_epi == 0 ? grouped_act(x, p.grp_act) : x * row_scale);
+            }
+        }
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           if constexpr (GATED) {
@@ -627,7 +666,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
           } else {
             const int o0 = n0 + c0 + h * 16;
-            OutT* dst = out + (int64_t)t * p.ldc + o0;
+            OutT* dst = out + t_out * p.ldc + o0;
             if (vec && o0 + 16 <= n_out) {
               uint4 w0, w1;
               __nv_bfloat162* h0 = reinterpret_cast<__nv_bfloat162*>(&w0);
@@ -811,7 +850,7 @@ DINFER_API int dinfer_gemm_tc_fused(const void* x, int64_t ldx, const void* w, i
     return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: the residual epilogue needs the norm's weight and room for the sums, and no gate");
   if (ss_in && (ss_parts <= 0 || ss_stride < tokens))
     return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: the scaled epilogue needs the parts of the sums (parts=%d stride=%d)", ss_parts, ss_stride);
-  GemmParams p;
+  GemmParams p = {};
   if (act < 0 || act > 2) return refuse(DINFER_BAD_ARGUMENT, "gemm_tc: unknown gate %d (0 none, 1 silu, 2 tanh-gelu)", act);
   p.act = act;
   p.resid = resid; p.ldr = ldr; p.norm_w = norm_w; p.norm_w_f32 = norm_w_f32; p.ss_out = ss_out;
@@ -850,6 +889,31 @@ DINFER_API int dinfer_gemm_tc_fused(const void* x, int64_t ldx, const void* w, i
   if ((rc = make_map(&mb, w, N, K, ldw, NT / 2))) return rc;
   if (act) return out_f32 ? launch_pair<float, true>(ma, mb, p, stream) : launch_pair<__nv_bfloat16, true>(ma, mb, p, stream);
   return out_f32 ? launch_pair<float, false>(ma, mb, p, stream) : launch_pair<__nv_bfloat16, false>(ma, mb, p, stream);
+}
+
+// Grouped product of a routed feed-forward's prompt-sized steps on the two-SM kernel: x [cap, K] holds the rows expert
+// by expert, every expert's run padded to a multiple of 256 (cap a multiple of 256), tile_expert [cap / 256] names the
+// expert of each 256-row tile (-1: none); w [E * N, K] holds the experts' matrices one behind the other.
+// epi 0: out [cap, N] = act(x w_e^T) row for row (act: 0 none, 1 relu squared, 2 silu, 3 tanh-gelu, 4 relu);
+// epi 1: out [pairs, N]: row t of the product, times row_w[sorted[t]], goes to row sorted[t] (sorted[t] >= pairs: padding).
+DINFER_API int dinfer_gemm_tc_grouped(const void* x, int64_t ldx, const void* w, void* out, int64_t ldc,
+                                      const int* tile_expert, const int* sorted, const float* row_w, int cap, int pairs,
+                                      int E, int N, int K, int epi, int act, int* status, cudaStream_t stream) {
+  if (cap <= 0 || cap % 256 || pairs < 0 || E <= 0 || N <= 0 || K <= 0 || !tile_expert || (epi != 0 && epi != 1) ||
+      (epi == 1 && (!sorted || !row_w)) || act < 0 || act > 4)
+    return refuse(DINFER_BAD_ARGUMENT, "gemm_tc_grouped: bad arguments cap=%d pairs=%d E=%d N=%d K=%d epi=%d", cap, pairs, E, N, K, epi);
+  if ((K % 8) || (ldx % 8) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
+    return refuse(DINFER_BAD_ARGUMENT, "gemm_tc_grouped: K and the row stride must be multiples of 8 and the bases 16-byte aligned (TMA)");
+  if (!status) return refuse(DINFER_BAD_ARGUMENT, "gemm_tc_grouped: a status word is required");
+  GemmParams p = {};
+  p.out = out; p.ldc = ldc; p.tokens = cap; p.N = N; p.K = K; p.status = status;
+  p.k_blocks_per_split = (K + BLOCK_K - 1) / BLOCK_K; p.splits = 1;
+  p.tile_expert = tile_expert; p.sorted = sorted; p.row_w = row_w; p.pairs = pairs; p.grp_epi = epi; p.grp_act = act;
+  CUtensorMap ma, mb;
+  int rc;
+  if ((rc = make_map(&ma, x, cap, K, ldx, TILE_M))) return rc;
+  if ((rc = make_map(&mb, w, (int64_t)E * N, K, K, NT / 2))) return rc;
+  return launch_pair<__nv_bfloat16, false>(ma, mb, p, stream);
 }
 
 DINFER_API int dinfer_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw, void* out, int64_t ldc,

@@ -331,6 +331,53 @@ moe_combine_kernel(const TA* __restrict__ y, const TA* __restrict__ shared, cons
   }
 }
 
+// bfloat16 rows of a multiple of 8 elements: 16-byte loads, one thread per 8 columns, the token's rows independent loads
+__global__ void __launch_bounds__(256)
+moe_combine_bf16x8_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ shared,
+                          const float* __restrict__ gate, __nv_bfloat16* __restrict__ out, int top, int h) {
+  pdl_enter();
+  const int t = blockIdx.x;
+  const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (i >= h) return;
+  float a[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) a[j] = 0.f;
+  auto add = [&](const __nv_bfloat16* row, float w) {
+    const uint4 v = *reinterpret_cast<const uint4*>(row + i);
+    const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(p2[j]); a[2 * j] += w * f.x; a[2 * j + 1] += w * f.y; }
+  };
+  for (int k = 0; k < top; ++k) add(y + ((int64_t)t * top + k) * h, 1.f);
+  if (shared) add(shared + (int64_t)t * h, gate ? gate[t] : 1.f);
+  uint4 o;
+  __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(a[2 * j], a[2 * j + 1]);
+  *reinterpret_cast<uint4*>(out + (int64_t)t * h + i) = o;
+}
+
+// a[pos] = x[sorted[pos] / top] (zeros for padding): the rows of a step laid out expert by expert, for products that
+// want every expert's rows side by side in memory
+template <typename TA>
+__global__ void __launch_bounds__(256)
+moe_gather_kernel(const TA* __restrict__ x, int64_t ldx, const int* __restrict__ sorted, TA* __restrict__ a, int pairs,
+                  int top, int h) {
+  pdl_enter();
+  const int pos = blockIdx.x;
+  const int pr = sorted[pos];
+  TA* dst = a + (int64_t)pos * h;
+  const TA* src = pr < pairs ? x + (int64_t)(pr / top) * ldx : nullptr;
+  const bool vec = sizeof(TA) == 2 && h % 8 == 0 && ldx % 8 == 0 && !(reinterpret_cast<uintptr_t>(x) & 15) &&
+                   !(reinterpret_cast<uintptr_t>(a) & 15);
+  if (vec) {
+    for (int i = threadIdx.x * 8; i < h; i += blockDim.x * 8)
+      *reinterpret_cast<uint4*>(dst + i) = src ? *reinterpret_cast<const uint4*>(src + i) : make_uint4(0, 0, 0, 0);
+  } else {
+    for (int i = threadIdx.x; i < h; i += blockDim.x) dst[i] = src ? src[i] : from_f32<TA>(0.f);
+  }
+}
+
 template <typename TA>
 __global__ void activation_kernel(const TA* __restrict__ x, TA* __restrict__ out, int64_t n, int act) {
   pdl_enter();
@@ -406,6 +453,12 @@ DINFER_API int dinfer_moe_combine(const void* y, const void* shared, const float
                                   int h, int act_dtype, cudaStream_t stream) {
   if (T < 0 || top <= 0 || h <= 0) return refuse(DINFER_BAD_ARGUMENT, "moe_combine: bad sizes T=%d top=%d h=%d", T, top, h);
   if (T == 0) return 0;
+  const auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  if (act_dtype == DINFER_BF16 && h % 8 == 0 && al(y) && al(shared) && al(out) && (h / 8 + 255) / 256 <= 65535) {
+    launch_pdl(moe_combine_bf16x8_kernel, dim3(T, (h / 8 + 255) / 256), dim3(256), 0, stream, (const __nv_bfloat16*)y,
+               (const __nv_bfloat16*)shared, gate, (__nv_bfloat16*)out, top, h);
+    return cuda_status("moe_combine");
+  }
   DINFER_DISPATCH_DTYPE(act_dtype, TA, {
     launch_pdl(moe_combine_kernel<TA>, dim3(T), dim3(256), 0, stream, (const TA*)y, (const TA*)shared, gate, (TA*)out,
                top, h);
@@ -422,6 +475,18 @@ DINFER_API int dinfer_activation(const void* x, void* out, int64_t n, int act, i
   DINFER_DISPATCH_DTYPE(act_dtype, TA, {
     launch_pdl(activation_kernel<TA>, dim3(blocks), dim3(256), 0, stream, (const TA*)x, (TA*)out, n, act);
     return cuda_status("activation");
+  });
+  return 0;
+}
+
+// x [T, h] rows of stride ldx; sorted [cap]; a [cap, h] contiguous.
+DINFER_API int dinfer_moe_gather(const void* x, int64_t ldx, const int* sorted, void* a, int cap, int pairs, int top, int h,
+                                 int act_dtype, cudaStream_t stream) {
+  if (cap < 0 || pairs < 0 || top <= 0 || h <= 0 || ldx < h) return refuse(DINFER_BAD_ARGUMENT, "moe_gather: bad sizes cap=%d h=%d", cap, h);
+  if (cap == 0) return 0;
+  DINFER_DISPATCH_DTYPE(act_dtype, TA, {
+    launch_pdl(moe_gather_kernel<TA>, dim3(cap), dim3(256), 0, stream, (const TA*)x, ldx, sorted, (TA*)a, pairs, top, h);
+    return cuda_status("moe_gather");
   });
   return 0;
 }

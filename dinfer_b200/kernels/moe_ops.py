@@ -14,7 +14,7 @@ ACTIVATIONS = {"none": 0, "relu2": 1, "silu": 2, "gelu_tanh": 3, "relu": 4}
 
 def route(logits: torch.Tensor, num_experts: int, top_k: int, scoring: str = "softmax", renormalize: bool = False,
           has_gate: bool = False) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
-    """From 32-bit router logits [T, E (+ 1)]: (expert ids int32 [T, top_k], weights f32 [T, top_k], gate f32 [T] or
+    """From 32-bit router logits [T, E (+ 1) or more columns]: (expert ids int32 [T, top_k], weights f32 [T, top_k], gate f32 [T] or
     None).  ``scoring`` softmax (over all experts) or sigmoid; the weights are the chosen scores, divided by their sum
     with ``renormalize``; ``has_gate``: column E holds a shared expert's gate logit, gate = its sigmoid."""
     require_cuda(logits)
@@ -22,8 +22,8 @@ def route(logits: torch.Tensor, num_experts: int, top_k: int, scoring: str = "so
     T = logits.shape[0]
     if scoring not in ("softmax", "sigmoid"):
         raise KernelError(f"moe route: unknown scoring {scoring!r}")
-    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.shape[1] != num_experts + int(has_gate):
-        raise KernelError("moe route: logits f32 [T, E (+ 1)]")
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.shape[1] < num_experts + int(has_gate):
+        raise KernelError("moe route: logits f32 [T, >= E (+ 1)]")
     ids = torch.empty((T, top_k), dtype=torch.int32, device=logits.device)
     weights = torch.empty((T, top_k), dtype=torch.float32, device=logits.device)
     gate = torch.empty((T,), dtype=torch.float32, device=logits.device) if has_gate else None
@@ -48,6 +48,57 @@ def router(h: torch.Tensor, w_router: torch.Tensor, top_k: int, scoring: str = "
 def row_tile(pairs: int, num_experts: int) -> int:
     """Rows of a tile of the grouped products: 16 while an expert gets few rows (decode steps), else 64."""
     return 16 if pairs <= 16 * num_experts else 64
+
+
+# rows of a tile of the two-SM tcgen05 kernel, and the average rows per expert from which the grouped products of a
+# step run on it (below, padding every expert's run to a whole tile costs more than the faster tensor path gains)
+TC_ROW_TILE = 256
+TC_MIN_ROWS_PER_EXPERT = 96
+
+
+def tc_grouped_supported(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, pairs: int) -> bool:
+    """Whether a step's grouped products can run on the tcgen05 kernel: bfloat16, rows TMA can address, and enough rows."""
+    E, ff, h = w_up.shape
+    return (x.dtype == torch.bfloat16 and w_up.dtype == torch.bfloat16 and w_down.dtype == torch.bfloat16
+            and h % 8 == 0 and ff % 8 == 0 and pairs >= TC_MIN_ROWS_PER_EXPERT * E
+            and w_up.data_ptr() % 16 == 0 and w_down.data_ptr() % 16 == 0)
+
+
+def gather_rows(x: torch.Tensor, sorted_: torch.Tensor, pairs: int, top_k: int) -> torch.Tensor:
+    """The step's rows laid out expert by expert: a[pos] = x[sorted[pos] // top_k], zeros where the layout pads."""
+    require_cuda(x, sorted_)
+    _rows_contiguous(x, "moe gather")
+    cap, h = sorted_.numel(), x.shape[1]
+    a = torch.empty((cap, h), dtype=x.dtype, device=x.device)
+    lib, f = _fn("moe", "dinfer_moe_gather", [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    check(lib, f(ptr(x), x.stride(0), ptr(sorted_), ptr(a), cap, pairs, top_k, h, dtype_code(x.dtype), stream_handle()),
+          "moe_gather")
+    return a
+
+
+def grouped_gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, sorted_: torch.Tensor, tile_expert: torch.Tensor,
+                    pairs: int, mode: int, activation: str = "none", weights: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The grouped product on the two-SM tcgen05 kernel (bfloat16; the layout padded to ``TC_ROW_TILE`` rows per
+    expert run).  a [cap, K] by position.  mode 0: ``out[pos] = act(a[pos] @ w[e]^T)`` (out [cap, N]); mode 1:
+    ``out[pair] = (a[pos] @ w[e]^T) * weights[pair]`` (out [pairs, N])."""
+    from . import gemm_ops
+    require_cuda(a, w, out, sorted_, tile_expert, weights)
+    E, N, K = w.shape
+    cap = sorted_.numel()
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or not w.is_contiguous() \
+            or tuple(a.shape) != (cap, K) or a.stride(1) != 1 or out.stride(1) != 1 or out.shape[1] != N \
+            or cap % TC_ROW_TILE or tile_expert.numel() != cap // TC_ROW_TILE:
+        raise KernelError("moe grouped_gemm_tc: bfloat16 a [cap, K], w [E, N, K], out [*, N]; cap in whole tiles")
+    if (mode == 0 and out.shape[0] != cap) or (mode == 1 and (out.shape[0] != pairs or weights is None
+                                                              or weights.dtype != torch.float32 or weights.numel() != pairs)):
+        raise KernelError("moe grouped_gemm_tc: row counts or weights do not fit the mode")
+    st = gemm_ops._state(a.device)
+    lib, f = _fn("gemm_tc", "dinfer_gemm_tc_grouped",
+                 [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                  c_int, c_int, c_int, c_void_p, c_void_p])
+    check(lib, f(ptr(a), a.stride(0), ptr(w), ptr(out), out.stride(0), ptr(tile_expert), ptr(sorted_), ptr(weights), cap,
+                 pairs, E, N, K, int(mode), ACTIVATIONS[activation], ptr(st["status"]), stream_handle()), "gemm_tc_grouped")
+    return out
 
 
 def align(ids: torch.Tensor, num_experts: int, tile: int) -> Tuple[torch.Tensor, torch.Tensor]:

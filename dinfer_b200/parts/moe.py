@@ -74,6 +74,10 @@ class MoE(FeedForward):
         router_w = tensors[self.names["router"]]
         if self.shared_ff and self.shared_gate:             # the gate's row rides behind the experts' rows
             router_w = torch.cat([router_w, tensors[self.names["s_gate"]].to(router_w.dtype).reshape(1, -1)])
+        # rows padded with zeros to a multiple of 8: the product's 32-bit output rows then start on 16-byte boundaries
+        pad = -router_w.shape[0] % 8
+        if pad:
+            router_w = torch.cat([router_w, router_w.new_zeros((pad, router_w.shape[1]))])
         self.router = Linear(router_w)
         ups = [tensors[self.names["up"].format(e=e)] for e in range(self.E)]
         downs = [tensors[self.names["down"].format(e=e)] for e in range(self.E)]
@@ -86,6 +90,8 @@ class MoE(FeedForward):
 
     def kernel_libraries(self):
         libs = ["moe"] + self.router.kernel_libraries()
+        if self.w_up.dtype == torch.bfloat16:
+            libs.append("gemm_tc")
         if self.shared_ff:
             libs += self.shared_up.kernel_libraries() + self.shared_down.kernel_libraries()
         return libs
@@ -97,16 +103,28 @@ class MoE(FeedForward):
         ids, weights, gate = moe_ops.route(z, self.E, self.top, self.scoring, self.renormalize,
                                            bool(self.shared_ff and self.shared_gate))
         pairs = T * self.top
+        if moe_ops.tc_grouped_supported(x, self.w_up, self.w_down, pairs):
+            # prompt-sized steps: rows laid out expert by expert in whole 256-row tiles, both products on tcgen05
+            order, tile_expert = moe_ops.align(ids, self.E, moe_ops.TC_ROW_TILE)
+            a = moe_ops.gather_rows(x, order, pairs, self.top)
+            u = torch.empty((order.numel(), self.ff), dtype=x.dtype, device=x.device)
+            moe_ops.grouped_gemm_tc(a, self.w_up, u, order, tile_expert, pairs, 0, self.activation)
+            y = torch.empty((pairs, self.hidden), dtype=x.dtype, device=x.device)
+            moe_ops.grouped_gemm_tc(u, self.w_down, y, order, tile_expert, pairs, 1, weights=weights)
+            return self._combine(x, y, gate)
         tile = moe_ops.row_tile(pairs, self.E)
         order, tile_expert = moe_ops.align(ids, self.E, tile)
         u = torch.empty((order.numel(), self.ff), dtype=x.dtype, device=x.device)
         moe_ops.grouped_gemm(x, self.w_up, u, order, tile_expert, pairs, self.top, tile, 0, self.activation)
         y = torch.empty((pairs, self.hidden), dtype=x.dtype, device=x.device)
         moe_ops.grouped_gemm(u, self.w_down, y, order, tile_expert, pairs, self.top, tile, 1, weights=weights)
+        return self._combine(x, y, gate)
+
+    def _combine(self, x, y, gate):
         shared = None
         if self.shared_ff:
             s = self.shared_up(x)
             moe_ops.activation(s, s, self.activation)
             shared = self.shared_down(s)
-        out = torch.empty((T, self.hidden), dtype=x.dtype, device=x.device)
+        out = torch.empty((x.shape[0], self.hidden), dtype=x.dtype, device=x.device)
         return moe_ops.combine(y, out, self.top, shared, gate)

@@ -207,7 +207,7 @@ def test_routed_feed_forward_against_plain_and_alone_against_batched(dtype, case
     part.bind({k: dev(v) for k, v in W.items()})
     plain = {k[2:]: v.double() for k, v in W.items()}
     mlp = {"router": {"experts": case["E"], "top": case["top"]}, "shared": {"ff": case["shared"]} if case["shared"] else None}
-    for T in (1, 3, 37, 150):
+    for T in (1, 3, 37, 150, 700):
         x = torch.randn(4 * T + 8, h, generator=g).to(dt)
         # rows whose choice of experts is decided (a gap to the first rejected expert that rounding cannot close)
         x = x[P.router_margin(x.double() @ plain["router"].T, case["top"]) > 0.2][:T]
