@@ -183,6 +183,53 @@ def test_latent_attention_far_keys_page_borders_and_the_causal_edge(dtype, kerne
         assert float(w[:, stand_out[p]].min()) > 0.5
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("kernel", ["generic", "tc"])
+def test_latent_attention_window_edges(dtype, kernel):
+    """The kernels' ``window`` (no layer of the design sets it; another design's may): the key just inside the window
+    carries the score that stands out for one query, the key just outside it a far larger one for another; prompt
+    rows and decoded tokens, several key splits."""
+    from dinfer_b200.kernels import latent_ops
+    Hh, R, Pd, page, window, n, scale = 4, 32, 16, 8, 100, 300, 0.3
+    if kernel == "tc" and dtype != "bfloat16":
+        pytest.skip("the tensor-core kernel takes bfloat16")
+    dt = DT[dtype]
+    g = torch.Generator().manual_seed(17)
+    W = R + Pd
+    rows = (torch.randn(n, W, generator=g) * 0.2).to(dt)
+    marks = torch.linalg.qr(torch.randn(W, 2, generator=g)).Q.T.contiguous()
+    qa, qb = 250, 299                                           # queries: one rests on the key just inside, one must not see the one just outside
+    rows[qa - window + 1] += (marks[0] * 3.0).to(dt)
+    rows[qb - window] += (marks[1] * 30.0).to(dt)
+    cache, table = scatter_into_pages(rows, page, random.Random(3))
+    q_all, pos_all, cu, seqs = [], [], [0], []
+    for last, mark in ((qa, marks[0]), (qb, marks[1])):
+        for pp in (range(last - 4, last + 1) if last == qa else [last]):
+            qv = torch.randn(Hh, W, generator=g) * 0.1
+            if pp == last:
+                qv += mark * 12.0
+            q_all.append(qv)
+            pos_all.append(pp)
+        cu.append(len(q_all))
+        seqs.append(last + 1)
+    q_lat = torch.stack(q_all).to(dt)
+    bt = torch.tensor([table, table], dtype=torch.int32)
+    out = torch.full((len(q_all), Hh, R), float("nan"), dtype=dt, device="cuda")
+    args = (dev(q_lat), out, dev(cache), dev(bt), dev(torch.tensor(cu, dtype=torch.int32)))
+    if kernel == "generic":
+        latent_ops.attention_latent_generic(*args, dev(torch.tensor(pos_all, dtype=torch.int32)), R, Pd, scale, window)
+    else:
+        latent_ops.attention_latent_tc(*args, dev(torch.tensor(seqs, dtype=torch.int32)), R, Pd, scale, window,
+                                       max_q_len=5, max_seq_len=n, splits=3)
+    for t, p in enumerate(pos_all):
+        s = (q_lat[t].double() @ rows.double().T) * scale
+        s[:, p + 1:] = float("-inf")
+        s[:, :max(0, p - window + 1)] = float("-inf")
+        close(out[t], torch.softmax(s, -1) @ rows.double()[:, :R], TOL[dtype])
+    w = torch.softmax((q_lat[4].double() @ rows.double().T * scale)[:, qa - window + 1:qa + 1], -1)
+    assert float(w[:, 0].min()) > 0.5
+
+
 MOE_CASES = [dict(E=5, top=1, ff=24, shared=40), dict(E=8, top=3, ff=16, shared=0), dict(E=1, top=1, ff=32, shared=8),
              dict(E=16, top=4, ff=64, shared=96), dict(E=7, top=7, ff=20, shared=12)]
 
