@@ -125,7 +125,7 @@ def scatter_into_pages(rows, page, rng, spare=3):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("kernel", ["generic", "tc"])
-@pytest.mark.parametrize("sizes", [(4, 32, 16, 16), (6, 64, 32, 8), (16, 128, 64, 32), (3, 48, 16, 4)])
+@pytest.mark.parametrize("sizes", [(4, 32, 16, 16), (7, 80, 48, 8), (16, 128, 64, 32), (3, 48, 16, 4)])
 def test_latent_attention_far_keys_page_borders_and_the_causal_edge(dtype, kernel, sizes):
     """One request of 700 cached rows in shuffled pages.  Among hundreds of small scores one key stands out for each
     query: a far one (position 2), the one on each side of a page border, the query's own position; the row just
@@ -231,7 +231,7 @@ def test_latent_attention_window_edges(dtype, kernel):
 
 
 MOE_CASES = [dict(E=5, top=1, ff=24, shared=40), dict(E=8, top=3, ff=16, shared=0), dict(E=1, top=1, ff=32, shared=8),
-             dict(E=16, top=4, ff=64, shared=96), dict(E=7, top=7, ff=20, shared=12)]
+             dict(E=12, top=4, ff=48, shared=80), dict(E=7, top=7, ff=20, shared=12)]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
