@@ -264,7 +264,7 @@ def test_routed_feed_forward_against_plain_and_alone_against_batched(dtype, case
         if T == 37:                                            # a token's row does not depend on its company
             for t in (0, 17, 36):
                 alone = part.forward(dev(x[t:t + 1].clone()))
-                close(alone[0], got[t], 1e-6 if dtype == "float32" else 1e-2)
+                close(alone[0], got[t], 1e-5 if dtype == "float32" else 1e-2)   # the order of the sums differs with the row count, nothing else
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
