@@ -53,7 +53,12 @@ MC = mixer(2, 12, 6, 20, 24, 20, base=100.0, rot_dims=4)
 DOBEDRA_C = {"architecture": "Dobedra", "vocab": 331, "width": 72, "norm": {"eps": 1e-6}, "logit_softcap": 12.0,
              "layers": [layer(MC, moe(4, 2, 28, shared=12)), layer(dict(MC, kv_from=0), dense(100)),
                         layer(mixer(3, 10, 2, 6, 14, 10, base=50.0), moe(7, 1, 20))]}
-CONFIGS = {"A": DOBEDRA_A, "B": DOBEDRA_B, "C": DOBEDRA_C}
+# a width no 16-byte load or tensor-core tile divides (every product and the grouped products take their plain paths in
+# bfloat16 too), many heads over a small latent
+MD = mixer(9, 20, 12, 28, 36, 44, base=2000.0)
+DOBEDRA_D = {"architecture": "Dobedra", "vocab": 257, "width": 100, "norm": {"eps": 2e-6}, "logit_softcap": 20.0,
+             "layers": [layer(MD, dense(52)), layer(dict(MD, kv_from=0), moe(5, 2, 36, shared=20))]}
+CONFIGS = {"A": DOBEDRA_A, "B": DOBEDRA_B, "C": DOBEDRA_C, "D": DOBEDRA_D}
 
 
 def write_model(path: str, cfg: dict, seed: int, dtype: torch.dtype, sharp: float = 6.0, std: float = 0.08) -> str:

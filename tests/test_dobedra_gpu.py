@@ -125,7 +125,7 @@ def scatter_into_pages(rows, page, rng, spare=3):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("kernel", ["generic", "tc"])
-@pytest.mark.parametrize("sizes", [(4, 32, 16, 16), (7, 80, 48, 8), (16, 128, 64, 32), (3, 48, 16, 4)])
+@pytest.mark.parametrize("sizes", [(4, 32, 16, 16), (7, 80, 48, 8), (16, 128, 64, 32), (3, 48, 16, 4), (16, 512, 64, 16), (20, 256, 32, 64)])
 def test_latent_attention_far_keys_page_borders_and_the_causal_edge(dtype, kernel, sizes):
     """One request of 700 cached rows in shuffled pages.  Among hundreds of small scores one key stands out for each
     query: a far one (position 2), the one on each side of a page border, the query's own position; the row just
@@ -310,7 +310,8 @@ def test_gated_feed_forward_with_the_tanh_gelu(dtype, rows):
 
 LENGTHS = {"A": {"a": 1, "b": 2, "c": 19, "d": 64, "e": 97, "f": 333},
            "B": {"a": 3, "b": 16, "c": 17, "d": 63, "e": 150, "f": 401},
-           "C": {"a": 2, "b": 33, "c": 129, "d": 260}}
+           "C": {"a": 2, "b": 33, "c": 129, "d": 260},
+           "D": {"a": 1, "b": 40, "c": 150}}
 
 
 class Oracle:
@@ -348,7 +349,7 @@ def decided_requests(name, model_dirs):
 
 @pytest.mark.parametrize("block_size", [4, 16, 64])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_replay_all_ways(model_dirs, name, dtype, block_size):
     """Every position of every request, whole / with a decoded tail long enough to pass page borders / in portions
     down to two tokens / mixed with up to four live requests on a pool that only holds the most demanding step, so
