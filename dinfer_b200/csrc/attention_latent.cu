@@ -200,7 +200,9 @@ struct LatentTcParams {
   float* ml;                     // [T * H, splits, 2] maximum (log2 domain) and sum
 };
 
-template <int MT, int NT>
+// NB: buffers of the key tile (2: the next tile is fetched while this one is worked on; 1: where 64 query rows of a wide
+// latent leave shared memory for one, so that a fetched tile serves twice as many rows)
+template <int MT, int NT, int NB>
 __global__ void __launch_bounds__(TC_THREADS)
 attention_latent_tc_kernel(const LatentTcParams p) {
   constexpr int BM = 16 * MT;
@@ -210,7 +212,7 @@ attention_latent_tc_kernel(const LatentTcParams p) {
   const int W = p.R + p.P, WS = W + 8;        // row of a tile in elements, and its padded stride
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __nv_bfloat16* Ks = Qs + (size_t)BM * WS;
-  __nv_bfloat16* Ps = Ks + (size_t)2 * TK * WS;
+  __nv_bfloat16* Ps = Ks + (size_t)NB * TK * WS;
   float* Ss = reinterpret_cast<float*>(Ps + BM * (TK + 8));
   float* m_s = Ss + BM * (TK + 4);
   float* l_s = m_s + BM;
@@ -221,14 +223,15 @@ attention_latent_tc_kernel(const LatentTcParams p) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   // which request and which of its row tiles
-  int b = 0, tile = blockIdx.x, n_q = 0;
+  int b = 0, tile = blockIdx.x, n_q = 0, tiles = 0;
   for (; b < p.num_reqs; ++b) {
     n_q = p.cu_seqlens[b + 1] - p.cu_seqlens[b];
-    const int tiles = n_q > 0 ? (n_q * p.H + BM - 1) / BM : 0;
+    tiles = n_q > 0 ? (n_q * p.H + BM - 1) / BM : 0;
     if (tile < tiles) break;
     tile -= tiles;
   }
   if (b >= p.num_reqs) return;
+  tile = tiles - 1 - tile;                                     // a request's last rows see the most keys: they start first
   const int t0 = p.cu_seqlens[b];
   const int rows = n_q * p.H;
   const int first_pos = p.seq_lens[b] - n_q;                   // position of the request's first new token
@@ -281,12 +284,16 @@ attention_latent_tc_kernel(const LatentTcParams p) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) o[mt][nt][e] = 0.f;
 
-  if (kt0 < kt1) load_tile(kt0, 0);
+  if (NB == 2 && kt0 < kt1) load_tile(kt0, 0);
   for (int kt = kt0; kt < kt1; ++kt) {
-    const int buf = (kt - kt0) & 1;
+    const int buf = NB == 2 ? (kt - kt0) & 1 : 0;
+    if (NB == 1) {
+      __syncthreads();                                         // everyone is done with the tile before
+      load_tile(kt, 0);
+    }
     cp_async_wait<0>();
     __syncthreads();                                           // tile kt landed; everyone is done with the other buffer
-    if (kt + 1 < kt1) load_tile(kt + 1, buf ^ 1);
+    if (NB == 2 && kt + 1 < kt1) load_tile(kt + 1, buf ^ 1);
     const __nv_bfloat16* Kt = Ks + (size_t)buf * TK * WS;
 
     // ---- S = Q K^T: this warp's 8 keys (one n-tile)
@@ -446,14 +453,14 @@ attention_latent_fold_kernel(const float* __restrict__ part, const float* __rest
   }
 }
 
-template <int MT, int NT>
+template <int MT, int NT, int NB = 2>
 int launch_tc(const LatentTcParams& p, int row_tiles, cudaStream_t stream) {
   constexpr int BM = 16 * MT;
   const int WS = p.R + p.P + 8;
-  const size_t smem = (size_t)BM * WS * 2 + (size_t)2 * TK * WS * 2 + (size_t)BM * (TK + 8) * 2 + (size_t)BM * (TK + 4) * 4 +
+  const size_t smem = (size_t)BM * WS * 2 + (size_t)NB * TK * WS * 2 + (size_t)BM * (TK + 8) * 2 + (size_t)BM * (TK + 4) * 4 +
                       (size_t)BM * 3 * 4 + (size_t)BM * 4 + 2 * TK * 4;
   if (smem > 227 * 1024) return refuse(DINFER_BAD_ARGUMENT, "attention_latent_tc: %zu bytes of shared memory", smem);
-  auto k = attention_latent_tc_kernel<MT, NT>;
+  auto k = attention_latent_tc_kernel<MT, NT, NB>;
   static size_t opted = 0;                     // the most this instantiation was opted in for (kept out of graph captures once set)
   if (smem > 48 * 1024 && smem > opted) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
@@ -469,8 +476,7 @@ int launch_tc(const LatentTcParams& p, int row_tiles, cudaStream_t stream) {
 // Most row tiles per SM-wide grid the caller should assume: BM rows per tile for these sizes.
 DINFER_API int dinfer_attention_latent_tc_rows(int R, int max_rows_per_req) {
   if (max_rows_per_req <= 16) return 16;
-  if (R > 256) return 32;                                    // a wider latent leaves shared memory for 32 query rows
-  return max_rows_per_req <= 32 ? 32 : 64;
+  return max_rows_per_req <= 32 ? 32 : 64;                   // 64 rows of a latent above 256: with one key-tile buffer
 }
 
 // bfloat16 only.  q [T, H, R + P] (ldq_t, ldq_h), out [T, H, R] (ldo_t, ldo_h), cache [pages, block_size, R + P];
@@ -502,7 +508,7 @@ DINFER_API int dinfer_attention_latent_tc(const void* q, int64_t ldq_t, int64_t 
 #define GO(MT, NT) rc = launch_tc<MT, NT>(p, row_tiles, stream)
   if (bm == 16) { if (nt <= 1) GO(1, 1); else if (nt <= 2) GO(1, 2); else if (nt <= 4) GO(1, 4); else GO(1, 8); }
   else if (bm == 32) { if (nt <= 1) GO(2, 1); else if (nt <= 2) GO(2, 2); else if (nt <= 4) GO(2, 4); else GO(2, 8); }
-  else { if (nt <= 1) GO(4, 1); else if (nt <= 2) GO(4, 2); else GO(4, 4); }
+  else { if (nt <= 1) GO(4, 1); else if (nt <= 2) GO(4, 2); else if (nt <= 4) GO(4, 4); else rc = launch_tc<4, 8, 1>(p, row_tiles, stream); }
 #undef GO
   if (rc != 0 || splits == 1) return rc;
   launch_pdl(attention_latent_fold_kernel, dim3(T * H), dim3(128), 0, stream, (const float*)part, (const float*)ml,

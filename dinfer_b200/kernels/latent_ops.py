@@ -115,11 +115,11 @@ def tc_row_tile(kv_rank: int, max_rows_per_req: int) -> int:
 
 
 def tc_splits(row_tiles: int, max_seq_len: int) -> int:
-    """CTAs that share the keys of a row tile: enough to give every SM four CTAs' worth of tiles in flight, each
-    CTA at least two key tiles long."""
+    """CTAs that share the keys of a row tile: enough to give every SM two CTAs' worth of tiles, each CTA at least
+    two key tiles long (a step with more row tiles than that shares nothing)."""
     from .lib import num_sms
     key_tiles = (max_seq_len + 63) // 64
-    want = (4 * num_sms() + row_tiles - 1) // max(1, row_tiles)
+    want = (2 * num_sms() + row_tiles - 1) // max(1, row_tiles)
     return max(1, min(want, key_tiles // 2, 64))
 
 
