@@ -223,16 +223,24 @@ attention_latent_tc_kernel(const LatentTcParams p) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   // which request and which of its row tiles
+  // the requests' offsets in one round of loads (a batch of up to 255 requests), not one dependent load per request
+  __shared__ int s_cu[TC_THREADS];
+  const bool cu_shared = p.num_reqs < TC_THREADS;
+  if (cu_shared) {
+    if (tid <= p.num_reqs) s_cu[tid] = p.cu_seqlens[tid];
+    __syncthreads();
+  }
+  const int* cu = cu_shared ? s_cu : p.cu_seqlens;
   int b = 0, tile = blockIdx.x, n_q = 0, tiles = 0;
   for (; b < p.num_reqs; ++b) {
-    n_q = p.cu_seqlens[b + 1] - p.cu_seqlens[b];
+    n_q = cu[b + 1] - cu[b];
     tiles = n_q > 0 ? (n_q * p.H + BM - 1) / BM : 0;
     if (tile < tiles) break;
     tile -= tiles;
   }
   if (b >= p.num_reqs) return;
   tile = tiles - 1 - tile;                                     // a request's last rows see the most keys: they start first
-  const int t0 = p.cu_seqlens[b];
+  const int t0 = cu[b];
   const int rows = n_q * p.H;
   const int first_pos = p.seq_lens[b] - n_q;                   // position of the request's first new token
   const int* table = p.block_table + (int64_t)b * p.max_blocks;
@@ -459,13 +467,13 @@ int launch_tc(const LatentTcParams& p, int row_tiles, cudaStream_t stream) {
   const int WS = p.R + p.P + 8;
   const size_t smem = (size_t)BM * WS * 2 + (size_t)NB * TK * WS * 2 + (size_t)BM * (TK + 8) * 2 + (size_t)BM * (TK + 4) * 4 +
                       (size_t)BM * 3 * 4 + (size_t)BM * 4 + 2 * TK * 4;
-  if (smem > 227 * 1024) return refuse(DINFER_BAD_ARGUMENT, "attention_latent_tc: %zu bytes of shared memory", smem);
+  if (smem > 225 * 1024) return refuse(DINFER_BAD_ARGUMENT, "attention_latent_tc: %zu bytes of shared memory", smem);
   auto k = attention_latent_tc_kernel<MT, NT, NB>;
   static size_t opted = 0;                     // the most this instantiation was opted in for (kept out of graph captures once set)
   if (smem > 48 * 1024 && smem > opted) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
     if (e != cudaSuccess) return refuse((int)e, "attention_latent_tc: shared memory opt-in failed: %s", cudaGetErrorString(e));
-    opted = 227 * 1024;
+    opted = 225 * 1024;
   }
   launch_pdl(k, dim3(row_tiles, p.splits), dim3(TC_THREADS), smem, stream, p);
   return cuda_status("attention_latent_tc");
