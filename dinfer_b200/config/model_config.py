@@ -369,3 +369,160 @@ class DobedraConfig:
         if self.eos_token_ids:
             d["eos_token_id"] = list(self.eos_token_ids)
         return d
+
+
+# ---------------------------------------------------------------- Zasipel
+
+@dataclass(frozen=True)
+class WindowAttentionSizes:
+    """Grouped-query attention over a sliding window with a sink: ``heads`` query heads and ``kv_heads`` key/value
+    heads of ``dim`` (queries, keys) and ``vdim`` (values) elements; the first ``rot_dims`` elements of a head rotate
+    (pairs 2i, 2i + 1; base ``rot_base``); a query sees itself and the ``window - 1`` tokens before it."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    window: int
+    rot_base: float
+    rot_dims: int
+
+    @classmethod
+    def from_dict(cls, m: Dict[str, Any], where: str) -> "WindowAttentionSizes":
+        rot, mask = _section(m, "rot", where), _section(m, "mask", where)
+        s = cls(heads=_take(m, "heads", int), kv_heads=_take(m, "kv_heads", int), dim=_take(m, "dim", int),
+                vdim=_take(m, "vdim", int), scale=_take(m, "scale", float), window=_take(mask, "size", int),
+                rot_base=_take(rot, "base", float), rot_dims=_take(rot, "dims", int))
+        for f in ("heads", "kv_heads", "dim", "vdim", "window"):
+            if getattr(s, f) <= 0:
+                raise ConfigError(f"config.json: {where}'{f}' must be positive, got {getattr(s, f)}")
+        if s.heads % s.kv_heads:
+            raise ConfigError(f"config.json: {where}heads {s.heads} must be a multiple of kv_heads {s.kv_heads}")
+        if s.rot_dims <= 0 or s.rot_dims % 2 or s.rot_dims > s.dim:
+            raise ConfigError(f"config.json: {where}rot.dims {s.rot_dims} must be even and at most dim {s.dim}")
+        if not s.rot_base > 0:
+            raise ConfigError(f"config.json: {where}rot.base must be positive")
+        return s
+
+    def to_dict(self) -> Dict[str, Any]:
+        return {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim, "scale": self.scale,
+                "mask": {"size": self.window}, "rot": {"base": self.rot_base, "dims": self.rot_dims}}
+
+
+@dataclass(frozen=True)
+class DeltaRuleSizes:
+    """A gated delta-rule mixer: ``heads`` value heads of ``vdim``, ``kv_heads`` query/key heads of ``dim``, short
+    convolutions of ``conv`` taps.  ``decay_rank`` / ``gate_rank``: the thin middle of the per-channel form's decay and
+    gate projections; the weight file decides them unless the configuration names them (optional keys, which the
+    random-weights mode needs)."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    conv: int
+    decay_rank: int = -1
+    gate_rank: int = -1
+
+    @classmethod
+    def from_dict(cls, m: Dict[str, Any], where: str) -> "DeltaRuleSizes":
+        s = cls(heads=_take(m, "heads", int), kv_heads=_take(m, "kv_heads", int), dim=_take(m, "dim", int),
+                vdim=_take(m, "vdim", int), conv=_take(m, "conv", int), decay_rank=_take(m, "decay_rank", int, -1),
+                gate_rank=_take(m, "gate_rank", int, -1))
+        for f in ("heads", "kv_heads", "dim", "vdim", "conv"):
+            if getattr(s, f) <= 0:
+                raise ConfigError(f"config.json: {where}'{f}' must be positive, got {getattr(s, f)}")
+        if s.heads % s.kv_heads:
+            raise ConfigError(f"config.json: {where}heads {s.heads} must be a multiple of kv_heads {s.kv_heads}")
+        if s.decay_rank == 0 or s.gate_rank == 0 or s.decay_rank < -1 or s.gate_rank < -1:
+            raise ConfigError(f"config.json: {where}decay_rank and gate_rank must be positive where given")
+        return s
+
+    def to_dict(self) -> Dict[str, Any]:
+        d = {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim, "conv": self.conv}
+        if self.decay_rank > 0:
+            d["decay_rank"] = self.decay_rank
+        if self.gate_rank > 0:
+            d["gate_rank"] = self.gate_rank
+        return d
+
+
+@dataclass(frozen=True)
+class ZasipelLayer:
+    """``type`` "parallel": ``left`` (window attention) and ``right`` (delta rule, one decay a head) side by side;
+    "channel_delta": ``right`` alone in its per-channel form.  ``mlp``: a routed feed-forward or none."""
+    type: str
+    left: Optional[WindowAttentionSizes]
+    right: DeltaRuleSizes
+    mlp: Optional[FeedForwardSizes]
+
+
+@dataclass(frozen=True)
+class ZasipelConfig:
+    """``config.json`` of a Zasipel model: ``vocab``, ``width``, ``norm.eps`` and the list ``layers``, each entry with
+    its ``type`` (the mixer it has), the mixer's sizes and its feed-forward (``mlp``: a mixture of experts chosen
+    by a table, or null).  ``max_positions`` is optional: the design has no longest sequence of its own."""
+    vocab: int
+    width: int
+    norm_eps: float
+    layers: Tuple[ZasipelLayer, ...]
+    max_positions: int = 1 << 20
+    eos_token_ids: Tuple[int, ...] = ()
+    architecture: str = "Zasipel"
+
+    MIXER_TYPES = ("parallel", "channel_delta")
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "ZasipelConfig":
+        raw = d.get("layers")
+        if not isinstance(raw, list) or not raw:
+            raise ConfigError("config.json: 'layers' must be a non-empty list")
+        layers = []
+        for i, l in enumerate(raw):
+            where = f"layers[{i}]: "
+            if not isinstance(l, dict):
+                raise ConfigError(f"config.json: {where}must be an object")
+            kind = _take(l, "type", str)
+            if kind not in cls.MIXER_TYPES:
+                raise ConfigError(f"config.json: {where}unknown type {kind!r} ({', '.join(cls.MIXER_TYPES)})")
+            mixer = _section(l, "mixer", where)
+            if kind == "parallel":
+                left = WindowAttentionSizes.from_dict(_section(mixer, "left", where), where + "left: ")
+                right = DeltaRuleSizes.from_dict(_section(mixer, "right", where), where + "right: ")
+            else:
+                left, right = None, DeltaRuleSizes.from_dict(mixer, where)
+            mlp = _section(l, "mlp", where, optional=True)
+            ff = FeedForwardSizes.from_dict(mlp, where) if mlp else None
+            if ff is not None and ff.kind != "moe":
+                raise ConfigError(f"config.json: {where}mlp.kind {ff.kind!r}: the design's feed-forward is a mixture of experts")
+            layers.append(ZasipelLayer(kind, left, right, ff))
+        eos = d.get("eos_token_id")
+        eos_ids = (eos,) if isinstance(eos, int) and not isinstance(eos, bool) else \
+            tuple(int(x) for x in eos) if isinstance(eos, (list, tuple)) else ()
+        cfg = cls(vocab=_take(d, "vocab", int), width=_take(d, "width", int),
+                  norm_eps=_take(_section(d, "norm", ""), "eps", float), layers=tuple(layers),
+                  max_positions=_take(d, "max_positions", int, 1 << 20), eos_token_ids=eos_ids,
+                  architecture=str(d.get("architecture") or (d.get("architectures") or ["Zasipel"])[0]))
+        if cfg.vocab <= 0 or cfg.width <= 0 or cfg.max_positions <= 1:
+            raise ConfigError("config.json: vocab, width and max_positions must be positive")
+        if not cfg.norm_eps > 0:
+            raise ConfigError(f"config.json: norm.eps must be positive, got {cfg.norm_eps}")
+        return cfg
+
+    def to_dict(self) -> Dict[str, Any]:
+        layers = []
+        for l in self.layers:
+            mixer = {"left": l.left.to_dict(), "right": l.right.to_dict()} if l.type == "parallel" else l.right.to_dict()
+            f = l.mlp
+            mlp = None
+            if f is not None:
+                mlp = {"kind": "moe", "expert": {"ff": f.ff}, "router": {"experts": f.experts, "top": f.top}}
+                if f.shared_ff:
+                    mlp["shared"] = {"ff": f.shared_ff}
+            layers.append({"type": l.type, "mixer": mixer, "mlp": mlp})
+        d = {"architecture": self.architecture, "vocab": self.vocab, "width": self.width,
+             "norm": {"eps": self.norm_eps}, "layers": layers}
+        if self.max_positions != 1 << 20:
+            d["max_positions"] = self.max_positions
+        if self.eos_token_ids:
+            d["eos_token_id"] = list(self.eos_token_ids)
+        return d

@@ -5,7 +5,9 @@
 // One warp owns one (token, query head): the lanes split the head's D elements, keys are visited
 // four at a time in position order with an online softmax; scores, softmax and the output sum are
 // 32-bit (expf, not the fast intrinsic).  A query at position p sees the keys [max(0, p-window+1), p]
-// of its own request, read through the request's block table.
+// of its own request, read through the request's block table.  Values may be Dv wide where keys are D wide (the
+// cache's rows are then Dc = max(D, Dv) wide); with `sink` the softmax has one more term of score 0 and no value:
+// p_j = exp(s_j) / (1 + sum exp(s_j)).
 //
 // Counterpart in the reference: the any-D reference kernels crates/kernels/cuda/gqa.cu:956-1118.
 #include "common.cuh"
@@ -17,12 +19,13 @@ namespace {
 constexpr int WARPS = 4;
 constexpr int KEYS = 4;
 
-template <typename T, int C>   // C = ceil(D / 32) elements per lane
+template <typename T, int C>   // C = ceil(max(D, Dv) / 32) elements per lane
 __global__ void __launch_bounds__(WARPS * 32)
 attention_generic_kernel(const T* __restrict__ q, int64_t ldq, T* __restrict__ out, int64_t ldo,
                          const T* __restrict__ cache, const int* __restrict__ block_table, int max_blocks,
                          const int* __restrict__ cu_seqlens, const int* __restrict__ positions,
-                         int num_reqs, int H, int Hkv, int D, int block_size, float scale, int window) {
+                         int num_reqs, int H, int Hkv, int D, int Dv, int Dc, int block_size, float scale, int window,
+                         int sink) {
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.y * WARPS + warp;
@@ -46,7 +49,7 @@ attention_generic_kernel(const T* __restrict__ q, int64_t ldq, T* __restrict__ o
     acc[c] = 0.f;
   }
   float m = -INFINITY, l = 0.f;
-  const int64_t plane = (int64_t)Hkv * block_size * D;       // one of k / v of one block
+  const int64_t plane = (int64_t)Hkv * block_size * Dc;      // one of k / v of one block
   for (int j0 = first; j0 <= pos; j0 += KEYS) {
     const T* kp[KEYS];
     float s[KEYS];
@@ -58,7 +61,7 @@ attention_generic_kernel(const T* __restrict__ q, int64_t ldq, T* __restrict__ o
       // a page the table does not hold (-1: a dummy row of a captured graph, a page a window has passed) is no key
       const int64_t blk = j <= pos ? table[j / block_size] : -1;
       if (blk >= 0) {
-        kp[u] = cache + blk * 2 * plane + ((int64_t)hk * block_size + j % block_size) * D;
+        kp[u] = cache + blk * 2 * plane + ((int64_t)hk * block_size + j % block_size) * Dc;
 #pragma unroll
         for (int c = 0; c < C; ++c) {
           const int e = lane + 32 * c;
@@ -85,34 +88,47 @@ attention_generic_kernel(const T* __restrict__ q, int64_t ldq, T* __restrict__ o
 #pragma unroll
         for (int c = 0; c < C; ++c) {
           const int e = lane + 32 * c;
-          if (e < D) acc[c] += p * to_f32<T>(vp[e]);
+          if (e < Dv) acc[c] += p * to_f32<T>(vp[e]);
         }
       }
     }
     m = m_new;
   }
+  if (sink) {                                                     // one more term, exp(0 - m), in the denominator only
+    const float m_new = fmaxf(m, 0.f);
+    const float alpha = m == -INFINITY ? 0.f : expf(m - m_new);
+    l = l * alpha + expf(-m_new);
+#pragma unroll
+    for (int c = 0; c < C; ++c) acc[c] *= alpha;
+  }
   const float inv = l > 0.f ? 1.f / l : 0.f;                      // a row without keys gives zeros
 #pragma unroll
   for (int c = 0; c < C; ++c) {
     const int e = lane + 32 * c;
-    if (e < D) out[(int64_t)t * ldo + (int64_t)h * D + e] = from_f32<T>(acc[c] * inv);
+    if (e < Dv) out[(int64_t)t * ldo + (int64_t)h * Dv + e] = from_f32<T>(acc[c] * inv);
   }
 }
 
 template <typename T, int C>
 int launch(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache, const int* block_table,
            int max_blocks, const int* cu_seqlens, const int* positions, int T_, int B, int H, int Hkv,
-           int D, int block_size, float scale, int window, cudaStream_t stream) {
+           int D, int Dv, int Dc, int block_size, float scale, int window, int sink, cudaStream_t stream) {
   dim3 grid(T_, (H + WARPS - 1) / WARPS);
   attention_generic_kernel<T, C><<<grid, WARPS * 32, 0, stream>>>(
       (const T*)q, ldq, (T*)out, ldo, (const T*)cache, block_table, max_blocks, cu_seqlens, positions,
-      B, H, Hkv, D, block_size, scale, window);
+      B, H, Hkv, D, Dv, Dc, block_size, scale, window, sink);
   return cuda_status("attention_generic");
 }
 
 }  // namespace
 
 DINFER_DEFINE_LAST_ERROR()
+
+DINFER_API int dinfer_attention_generic_ex(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
+                                           const int* block_table, int max_blocks, const int* cu_seqlens,
+                                           const int* positions, int T, int B, int H, int Hkv, int D, int Dv, int Dc,
+                                           int block_size, float scale, int window, int sink, int dtype,
+                                           cudaStream_t stream);
 
 // q: [T, ...] rows of stride ldq, head h at h*D; out likewise with stride ldo.
 // cache [num_blocks, 2, Hkv, block_size, D]; block_table [B, max_blocks] int32;
@@ -123,16 +139,27 @@ DINFER_API int dinfer_attention_generic(const void* q, int64_t ldq, void* out, i
                                         const int* positions, int T, int B, int H, int Hkv, int D,
                                         int block_size, float scale, int window, int dtype,
                                         cudaStream_t stream) {
+  return dinfer_attention_generic_ex(q, ldq, out, ldo, cache, block_table, max_blocks, cu_seqlens, positions, T, B, H,
+                                     Hkv, D, D, D, block_size, scale, window, 0, dtype, stream);
+}
+
+// The same with values Dv wide in a cache whose rows are Dc wide (out: head h at h*Dv), and an optional sink.
+DINFER_API int dinfer_attention_generic_ex(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
+                                           const int* block_table, int max_blocks, const int* cu_seqlens,
+                                           const int* positions, int T, int B, int H, int Hkv, int D, int Dv, int Dc,
+                                           int block_size, float scale, int window, int sink, int dtype,
+                                           cudaStream_t stream) {
+  if (Dv <= 0 || Dc < D || Dc < Dv) return refuse(DINFER_BAD_ARGUMENT, "attention_generic: bad sizes D=%d Dv=%d Dc=%d", D, Dv, Dc);
   if (T < 0 || B <= 0 || H <= 0 || Hkv <= 0 || D <= 0 || block_size <= 0 || max_blocks <= 0)
     return refuse(DINFER_BAD_ARGUMENT, "attention_generic: bad sizes T=%d B=%d H=%d Hkv=%d D=%d block=%d",
                   T, B, H, Hkv, D, block_size);
   if (H % Hkv) return refuse(DINFER_BAD_ARGUMENT, "attention_generic: heads %d not divisible by kv heads %d", H, Hkv);
-  if (D > 512) return refuse(DINFER_BAD_ARGUMENT, "attention_generic: head_dim %d above the limit 512", D);
+  if (D > 512 || Dv > 512) return refuse(DINFER_BAD_ARGUMENT, "attention_generic: head_dim %d / %d above the limit 512", D, Dv);
   if ((H + WARPS - 1) / WARPS > 65535) return refuse(DINFER_BAD_ARGUMENT, "attention_generic: too many heads");
   if (T == 0) return 0;
-  const int c = (D + 31) / 32;
+  const int c = ((D > Dv ? D : Dv) + 31) / 32;
 #define GO(C) return launch<T_, C>(q, ldq, out, ldo, cache, block_table, max_blocks, cu_seqlens, positions, \
-                                   T, B, H, Hkv, D, block_size, scale, window, stream)
+                                   T, B, H, Hkv, D, Dv, Dc, block_size, scale, window, sink, stream)
   DINFER_DISPATCH_DTYPE(dtype, T_, {
     if (c <= 1) GO(1);
     else if (c <= 2) GO(2);

@@ -41,6 +41,7 @@ LIBRARIES: Dict[str, tuple] = {
     "latent_post": ("latent_post.cu", []),
     "attention_latent": ("attention_latent.cu", []),
     "moe": ("moe.cu", []),
+    "delta_rule": ("delta_rule.cu", []),
     # host-side bookkeeping (page pools, cache manager, decode plans): plain C++, no CUDA
     "host_core": ("host_core.cpp", []),
 }

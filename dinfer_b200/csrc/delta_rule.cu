@@ -1,0 +1,293 @@
+// The gated delta rule: a recurrent mixer whose per-request state is a matrix S [key channels, value channels]
+// per head, in 32-bit, plus the last (taps - 1) inputs of a short causal convolution.
+//
+//   delta_prep        per token: short convolution (+ silu) of the q / k / v projections, reading what the
+//                     convolution needs from before the step out of the request's state; q and k made unit vectors
+//                     per head (q also times dk^-1/2); beta = sigmoid(b); decay g = exp(-exp(A_log) * softplus(a + dt_bias)),
+//                     one per head or one per head and key channel.  All results 32-bit.
+//   delta_conv_state  per request: the step's last (taps - 1) convolution inputs become the state's.
+//   delta_recurrence  per (request, head, group of value columns), token by token:
+//                         S <- g * S;  u = beta * (v - S^T k);  S <- S + k u^T;  o = S^T q
+//                     The columns of S are independent of one another, so a warp owns a few columns and the lanes
+//                     of a column share its rows; nothing but the order of a sum depends on how a request's tokens
+//                     are cut into steps, and the state between two steps is exact.
+//   delta_post        per (token, head): o / rms(o) * w * act(gate), rounded to the activation type.
+//
+// A request whose `fresh` flag is set starts from a zero state (nothing is read from its slot).
+#include "common.cuh"
+
+using namespace dinfer;
+
+namespace {
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+__device__ __forceinline__ int request_of(const int* __restrict__ cu, int B, int t) {
+  int lo = 0, hi = B - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (cu[mid] <= t) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+// ---------------------------------------------------------------- prep
+// P [T, ldp]: columns q (G*dk) at cq, k (G*dk) at ck, v (H*dv) at cv, b (H) at cb.  A [T, lda]: the decay's input,
+// H or H*dk wide.  conv_w [C, taps] with C = 2*G*dk + H*dv (q, k, v order).  hist [slots, hist_stride] (taps-1 rows of C).
+template <typename TA>
+__global__ void __launch_bounds__(256)
+delta_prep_kernel(const TA* __restrict__ P, int64_t ldp, int cq, int ck, int cv, int cb, const TA* __restrict__ A,
+                  int64_t lda, const float* __restrict__ conv_w, const float* __restrict__ A_log,
+                  const float* __restrict__ dt_bias, const float* __restrict__ hist, int64_t hist_stride,
+                  const int* __restrict__ cu, const int* __restrict__ slots, const int* __restrict__ fresh, int B,
+                  float* __restrict__ qn, float* __restrict__ kn, float* __restrict__ vv, float* __restrict__ beta,
+                  float* __restrict__ decay, int H, int G, int dk, int dv, int taps, int per_channel) {
+  extern __shared__ float y[];                             // the token's q | k channels after convolution and silu
+  pdl_enter();
+  const int t = blockIdx.x;
+  const int b = request_of(cu, B, t);
+  const int i = t - cu[b];                                 // index inside the step's portion
+  const bool have_hist = !fresh[b];
+  const float* hb = hist + (int64_t)slots[b] * hist_stride;
+  const int nq = G * dk, nv = H * dv, C = 2 * nq + nv;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const int col = c < nq ? cq + c : (c < 2 * nq ? ck + c - nq : cv + c - 2 * nq);
+    float acc = 0.f;
+    for (int d = 0; d < taps; ++d) {                       // d tokens back
+      float x = 0.f;
+      if (i - d >= 0) x = to_f32<TA>(P[(int64_t)(t - d) * ldp + col]);
+      else if (have_hist) x = hb[(int64_t)(taps - 1 + i - d) * C + c];
+      acc = fmaf(conv_w[(int64_t)c * taps + taps - 1 - d], x, acc);
+    }
+    const float s = silu_f(acc);
+    if (c < 2 * nq) y[c] = s; else vv[(int64_t)t * nv + c - 2 * nq] = s;
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+  for (int hd = warp; hd < 2 * G; hd += nwarp) {           // q heads, then k heads
+    const float* x = y + hd * dk;
+    float ss = 0.f;
+    for (int e = lane; e < dk; e += 32) ss += x[e] * x[e];
+    ss = warp_sum(ss);
+    float r = 1.f / sqrtf(ss + 1e-6f);
+    if (hd < G) r *= 1.f / sqrtf((float)dk);
+    float* o = hd < G ? qn + (int64_t)t * nq + hd * dk : kn + (int64_t)t * nq + (hd - G) * dk;
+    for (int e = lane; e < dk; e += 32) o[e] = x[e] * r;
+  }
+  for (int h = threadIdx.x; h < H; h += blockDim.x)
+    beta[(int64_t)t * H + h] = sigmoid_f(to_f32<TA>(P[(int64_t)t * ldp + cb + h]));
+  const int nd = per_channel ? H * dk : H;
+  for (int c = threadIdx.x; c < nd; c += blockDim.x) {
+    const int h = per_channel ? c / dk : c;
+    const float a = to_f32<TA>(A[(int64_t)t * lda + c]) + dt_bias[c];
+    decay[(int64_t)t * nd + c] = expf(-expf(A_log[h]) * softplus_f(a));
+  }
+}
+
+// the step's last (taps - 1) inputs of every channel become the request's history (rows oldest first)
+template <typename TA>
+__global__ void __launch_bounds__(256)
+delta_conv_state_kernel(const TA* __restrict__ P, int64_t ldp, int cq, int ck, int cv, float* __restrict__ hist,
+                        int64_t hist_stride, const int* __restrict__ cu, const int* __restrict__ slots,
+                        const int* __restrict__ fresh, int nq, int nv, int taps) {
+  pdl_enter();
+  const int b = blockIdx.x;
+  const int start = cu[b], n = cu[b + 1] - start;
+  if (n <= 0) return;
+  const bool have_hist = !fresh[b];
+  float* hb = hist + (int64_t)slots[b] * hist_stride;
+  const int C = 2 * nq + nv, rows = taps - 1;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+    const int col = c < nq ? cq + c : (c < 2 * nq ? ck + c - nq : cv + c - 2 * nq);
+    for (int r = 0; r < rows; ++r) {                       // rising r: a row is read (r + n) before it is overwritten
+      const int i = n - rows + r;                          // index inside the portion; negative: from the old history
+      float x = 0.f;
+      if (i >= 0) x = to_f32<TA>(P[(int64_t)(start + i) * ldp + col]);
+      else if (have_hist) x = hb[(int64_t)(rows + i) * C + c];
+      hb[(int64_t)r * C + c] = x;
+    }
+  }
+}
+
+// ---------------------------------------------------------------- recurrence
+// A block is WARPS warps over one (request, head): a warp owns COLS = 32 / LPC value columns, the LPC lanes of a column
+// own the rows i = lane_in_column (mod LPC).  S lives in shared memory while the block walks the request's tokens, a
+// tile of TT tokens' q, k, decay staged in shared memory at a time.
+constexpr int R_WARPS = 4;
+constexpr int R_TT = 8;
+
+template <int LPC>
+__global__ void __launch_bounds__(R_WARPS * 32)
+delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vv,
+                        const float* __restrict__ beta, const float* __restrict__ decay, float* __restrict__ state,
+                        int64_t state_stride, const int* __restrict__ cu, const int* __restrict__ slots,
+                        const int* __restrict__ fresh, float* __restrict__ out, int H, int G, int dk, int dv,
+                        int per_channel) {
+  constexpr int COLS = 32 / LPC, BC = COLS * R_WARPS;      // columns a warp / a block owns
+  // row stride of S: a warp's lanes (column c, row share s) touch s * SB + c, which must fall into 32 different banks
+  constexpr int SB = LPC > 1 ? BC + COLS : BC;
+  extern __shared__ float sm[];
+  float* S = sm;                                           // [dk][SB]
+  float* sq = S + (size_t)dk * SB;                         // [TT][dk]
+  float* sk = sq + (size_t)R_TT * dk;
+  float* sg = sk + (size_t)R_TT * dk;                      // [TT][dk] or [TT]
+  pdl_enter();
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int start = cu[b], n = cu[b + 1] - start;
+  if (n <= 0) return;
+  const int c0 = blockIdx.x * BC;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int lc = warp * COLS + lane / LPC, sub = lane % LPC;   // column inside the block, share of the rows
+  const int col = c0 + lc;
+  const bool live = col < dv;
+  const int g = h / (H / G);
+  float* Sg = state + (int64_t)slots[b] * state_stride + (int64_t)h * dk * dv;
+  const bool have = !fresh[b];
+  for (int idx = threadIdx.x; idx < dk * BC; idx += blockDim.x) {
+    const int i = idx / BC, c = idx % BC;
+    S[i * SB + c] = (have && c0 + c < dv) ? Sg[(int64_t)i * dv + c0 + c] : 0.f;
+  }
+  const int nq = G * dk, nd = per_channel ? H * dk : H;
+  for (int t0 = 0; t0 < n; t0 += R_TT) {
+    const int tt = min(R_TT, n - t0);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < tt * dk; idx += blockDim.x) {
+      const int j = idx / dk, e = idx % dk;
+      const int64_t t = start + t0 + j;
+      sq[idx] = qn[t * nq + g * dk + e];
+      sk[idx] = kn[t * nq + g * dk + e];
+      if (per_channel) sg[idx] = decay[t * nd + h * dk + e];
+    }
+    if (!per_channel)
+      for (int j = threadIdx.x; j < tt; j += blockDim.x) sg[j] = decay[(int64_t)(start + t0 + j) * nd + h];
+    __syncthreads();
+    for (int j = 0; j < tt; ++j) {
+      const int64_t t = start + t0 + j;
+      const float* q = sq + j * dk;
+      const float* k = sk + j * dk;
+      const float gs = per_channel ? 0.f : sg[j];
+      const float* gc = sg + j * dk;
+      float read = 0.f;
+      for (int i = sub; i < dk; i += LPC) {
+        const float s = S[i * SB + lc] * (per_channel ? gc[i] : gs);
+        S[i * SB + lc] = s;
+        read = fmaf(s, k[i], read);
+      }
+#pragma unroll
+      for (int o = 1; o < LPC; o <<= 1) read += __shfl_xor_sync(0xffffffffu, read, o);
+      const float v = live ? vv[t * ((int64_t)H * dv) + (int64_t)h * dv + col] : 0.f;
+      const float u = beta[t * H + h] * (v - read);
+      float acc = 0.f;
+      for (int i = sub; i < dk; i += LPC) {
+        const float s = fmaf(k[i], u, S[i * SB + lc]);
+        S[i * SB + lc] = s;
+        acc = fmaf(s, q[i], acc);
+      }
+#pragma unroll
+      for (int o = 1; o < LPC; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (live && sub == 0) out[t * ((int64_t)H * dv) + (int64_t)h * dv + col] = acc;
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < dk * BC; idx += blockDim.x) {
+    const int i = idx / BC, c = idx % BC;
+    if (c0 + c < dv) Sg[(int64_t)i * dv + c0 + c] = S[i * SB + c];
+  }
+}
+
+// ---------------------------------------------------------------- output norm and gate
+// one warp per (token, head): y = o * rsqrt(mean(o^2) + eps) * w * act(gate)
+template <typename TA>
+__global__ void __launch_bounds__(128)
+delta_post_kernel(const float* __restrict__ o, const float* __restrict__ w, const TA* __restrict__ gate, int64_t ldg,
+                  TA* __restrict__ y, int64_t ldy, int T, int H, int dv, float eps, int sigmoid_gate) {
+  pdl_enter();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t p = (int64_t)blockIdx.x * 4 + warp;
+  if (p >= (int64_t)T * H) return;
+  const int64_t t = p / H;
+  const int h = (int)(p % H);
+  const float* x = o + p * dv;
+  float ss = 0.f;
+  for (int e = lane; e < dv; e += 32) ss += x[e] * x[e];
+  ss = warp_sum(ss);
+  const float r = 1.f / sqrtf(ss / (float)dv + eps);
+  for (int e = lane; e < dv; e += 32) {
+    const float z = to_f32<TA>(gate[t * ldg + (int64_t)h * dv + e]);
+    const float a = sigmoid_gate ? sigmoid_f(z) : silu_f(z);
+    y[t * ldy + (int64_t)h * dv + e] = from_f32<TA>(x[e] * r * w[e] * a);
+  }
+}
+
+}  // namespace
+
+DINFER_DEFINE_LAST_ERROR()
+
+DINFER_API int dinfer_delta_prep(const void* P, int64_t ldp, int cq, int ck, int cv, int cb, const void* A, int64_t lda,
+                                 const float* conv_w, const float* A_log, const float* dt_bias, float* hist,
+                                 int64_t hist_stride, const int* cu, const int* slots, const int* fresh, int B,
+                                 float* qn, float* kn, float* vv, float* beta, float* decay, int T, int H, int G, int dk,
+                                 int dv, int taps, int per_channel, int act_dtype, cudaStream_t stream) {
+  if (T < 0 || B <= 0 || H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || taps <= 0)
+    return refuse(DINFER_BAD_ARGUMENT, "delta_prep: bad sizes T=%d B=%d H=%d G=%d dk=%d dv=%d taps=%d", T, B, H, G, dk, dv, taps);
+  const size_t smem = (size_t)2 * G * dk * sizeof(float);
+  if (smem > 200 * 1024) return refuse(DINFER_BAD_ARGUMENT, "delta_prep: %d key channels above the limit", 2 * G * dk);
+  if (T == 0) return 0;
+  const int nq = G * dk, nv = H * dv;
+  DINFER_DISPATCH_DTYPE(act_dtype, TA, {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(delta_prep_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_pdl(delta_prep_kernel<TA>, dim3(T), dim3(256), smem, stream, (const TA*)P, ldp, cq, ck, cv, cb, (const TA*)A,
+               lda, conv_w, A_log, dt_bias, (const float*)hist, hist_stride, cu, slots, fresh, B, qn, kn, vv, beta,
+               decay, H, G, dk, dv, taps, per_channel);
+    if (cudaError_t e = cudaGetLastError(); e != cudaSuccess) return refuse((int)e, "delta_prep: %s", cudaGetErrorString(e));
+    if (taps > 1) {
+      const int C = 2 * nq + nv;
+      int by = (C + 255) / 256;
+      if (by > 64) by = 64;
+      launch_pdl(delta_conv_state_kernel<TA>, dim3(B, by), dim3(256), 0, stream, (const TA*)P, ldp, cq, ck, cv, hist,
+                 hist_stride, cu, slots, fresh, nq, nv, taps);
+    }
+    return cuda_status("delta_prep");
+  });
+  return 0;
+}
+
+DINFER_API int dinfer_delta_recurrence(const float* qn, const float* kn, const float* vv, const float* beta,
+                                       const float* decay, float* state, int64_t state_stride, const int* cu,
+                                       const int* slots, const int* fresh, float* out, int B, int H, int G, int dk,
+                                       int dv, int per_channel, cudaStream_t stream) {
+  if (B <= 0 || H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || H > 65535 || B > 65535)
+    return refuse(DINFER_BAD_ARGUMENT, "delta_recurrence: bad sizes B=%d H=%d G=%d dk=%d dv=%d", B, H, G, dk, dv);
+  // lanes that share a column: enough that a lane owns about 16 rows, fewer for a narrow state
+  const int lpc = dk >= 128 ? 8 : (dk >= 48 ? 4 : (dk >= 24 ? 2 : 1));
+  const int bc = 32 / lpc * R_WARPS;
+  const int sb = lpc > 1 ? bc + 32 / lpc : bc;
+  const size_t smem = ((size_t)dk * sb + (size_t)R_TT * dk * 3) * sizeof(float);
+  if (smem > 200 * 1024) return refuse(DINFER_BAD_ARGUMENT, "delta_recurrence: %d key channels above the limit", dk);
+  dim3 grid((dv + bc - 1) / bc, H, B);
+#define GO(LPC_)                                                                                                   \
+  do {                                                                                                             \
+    if (smem > 48 * 1024)                                                                                          \
+      cudaFuncSetAttribute(delta_recurrence_kernel<LPC_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    launch_pdl(delta_recurrence_kernel<LPC_>, grid, dim3(R_WARPS * 32), smem, stream, qn, kn, vv, beta, decay,     \
+               state, state_stride, cu, slots, fresh, out, H, G, dk, dv, per_channel);                             \
+  } while (0)
+  if (lpc == 8) GO(8); else if (lpc == 4) GO(4); else if (lpc == 2) GO(2); else GO(1);
+#undef GO
+  return cuda_status("delta_recurrence");
+}
+
+DINFER_API int dinfer_delta_post(const float* o, const float* w, const void* gate, int64_t ldg, void* y, int64_t ldy,
+                                 int T, int H, int dv, float eps, int sigmoid_gate, int act_dtype, cudaStream_t stream) {
+  if (T < 0 || H <= 0 || dv <= 0) return refuse(DINFER_BAD_ARGUMENT, "delta_post: bad sizes T=%d H=%d dv=%d", T, H, dv);
+  if (T == 0) return 0;
+  const int64_t blocks = ((int64_t)T * H + 3) / 4;
+  DINFER_DISPATCH_DTYPE(act_dtype, TA, {
+    launch_pdl(delta_post_kernel<TA>, dim3((unsigned)blocks), dim3(128), 0, stream, o, w, (const TA*)gate, ldg, (TA*)y, ldy,
+               T, H, dv, eps, sigmoid_gate);
+    return cuda_status("delta_post");
+  });
+  return 0;
+}

@@ -88,6 +88,24 @@ moe_route_kernel(const float* __restrict__ logits, int64_t ldz, int* __restrict_
   }
 }
 
+// ---------------------------------------------------------------- routing without a router
+// A table [vocab, top] names each token id's experts; every choice weighs 1 / top.  A token id -(r + 1) stands for
+// prev[r] (a token the previous step sampled, still on the device).  An entry outside [0, E) becomes E: no expert.
+__global__ void __launch_bounds__(256)
+moe_route_table_kernel(const int* __restrict__ tokens, const int* __restrict__ prev, int n_prev,
+                       const int* __restrict__ table, int vocab, int* __restrict__ ids, float* __restrict__ weights,
+                       int T, int E, int top) {
+  pdl_enter();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= T * top) return;
+  int tok = tokens[i / top];
+  if (tok < 0) tok = (prev && -tok - 1 < n_prev) ? prev[-tok - 1] : 0;
+  int e = tok < vocab ? table[(int64_t)tok * top + i % top] : E;
+  if (e < 0 || e >= E) e = E;
+  ids[i] = e;
+  weights[i] = 1.f / (float)top;
+}
+
 // ---------------------------------------------------------------- pairs laid out expert by expert
 // sorted[pos] = pair index (t * top + k) or `pairs` for padding; tile_expert[tile] = expert of the tile or -1
 __global__ void __launch_bounds__(1024)
@@ -400,6 +418,17 @@ DINFER_API int dinfer_moe_route(const float* logits, int64_t ldz, int* ids, floa
   launch_pdl(moe_route_kernel, dim3((T + RW - 1) / RW), dim3(RW * 32), (size_t)RW * E * sizeof(float), stream, logits, ldz,
              ids, weights, gate, T, E, top, sigmoid_scores, renorm);
   return cuda_status("moe_route");
+}
+
+// tokens [T] int32 (negative: -(r + 1) names prev[r]); table [vocab, top] int32; ids, weights [T, top].
+DINFER_API int dinfer_moe_route_table(const int* tokens, const int* prev, int n_prev, const int* table, int vocab,
+                                      int* ids, float* weights, int T, int E, int top, cudaStream_t stream) {
+  if (T < 0 || E <= 0 || top <= 0 || vocab <= 0)
+    return refuse(DINFER_BAD_ARGUMENT, "moe_route_table: bad sizes T=%d E=%d top=%d vocab=%d", T, E, top, vocab);
+  if (T == 0) return 0;
+  launch_pdl(moe_route_table_kernel, dim3((T * top + 255) / 256), dim3(256), 0, stream, tokens, prev, n_prev, table,
+             vocab, ids, weights, T, E, top);
+  return cuda_status("moe_route_table");
 }
 
 // ids [pairs]; sorted [cap], cap >= pairs + E * (BM - 1) rounded up to BM; tile_expert [cap / BM].

@@ -347,3 +347,93 @@ DINFER_API int dinfer_scaled_add(float* residual, const void* d1, const void* s1
     }));
   return 0;
 }
+
+// A branch output that is normed before it joins the residual stream (a layer with its norm on the sublayer's
+// output), and the mean of two branches that are each normed first (two mixers side by side):
+//
+//   y      = a                                   one branch, no inner norm (w_a null)
+//          = coef * (rms(a) * w_a + rms(b) * w_b)   two branches, each divided by its own root mean square (b may be null)
+//   z      = y / sqrt(mean(y^2) + eps) * w       the outer norm (w null: z = y)
+//   residual += z                                (residual null: z goes to out32)
+//   cast   = T(residual)                         (optional: the stream in the activation type, for the next product)
+//
+// All of it in 32-bit, the row kept in shared memory.  One block per row.
+namespace {
+
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(1024)
+branch_norm_kernel(const TA* __restrict__ a, const TW* __restrict__ wa, const TA* __restrict__ b,
+                   const TW* __restrict__ wb, float coef, float inner_eps, const TW* __restrict__ w, float eps,
+                   float* __restrict__ residual, float* __restrict__ out32, TA* __restrict__ cast, int h) {
+  extern __shared__ float row[];
+  __shared__ float red[33];
+  pdl_enter();
+  const int64_t r = blockIdx.x;
+  const TA* pa = a + r * h;
+  const TA* pb = b ? b + r * h : nullptr;
+  float sa = 0.f, sb = 0.f;
+  if (wa) {
+    for (int i = threadIdx.x; i < h; i += blockDim.x) {
+      const float x = to_f32<TA>(pa[i]);
+      sa += x * x;
+      if (pb) { const float y = to_f32<TA>(pb[i]); sb += y * y; }
+    }
+    sa = block_sum(sa, red);
+    if (pb) sb = block_sum(sb, red);
+  }
+  const float ra = wa ? 1.f / sqrtf(sa / (float)h + inner_eps) : 1.f;
+  const float rb = pb ? 1.f / sqrtf(sb / (float)h + inner_eps) : 0.f;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < h; i += blockDim.x) {
+    float y = to_f32<TA>(pa[i]);
+    if (wa) {
+      y = y * ra * to_f32<TW>(wa[i]);
+      if (pb) y += to_f32<TA>(pb[i]) * rb * to_f32<TW>(wb[i]);
+      y *= coef;
+    }
+    row[i] = y;
+    ss += y * y;
+  }
+  float rn = 1.f;
+  if (w) rn = 1.f / sqrtf(block_sum(ss, red) / (float)h + eps);
+  for (int i = threadIdx.x; i < h; i += blockDim.x) {
+    float z = row[i];
+    if (w) z = z * rn * to_f32<TW>(w[i]);
+    if (residual) {
+      z += residual[r * h + i];
+      residual[r * h + i] = z;
+    } else {
+      out32[r * h + i] = z;
+    }
+    if (cast) cast[r * h + i] = from_f32<TA>(z);
+  }
+}
+
+}  // namespace
+
+// a, b [num_rows, h] act dtype (b null: one branch); wa, wb inner weights [h] (wa null: no inner norm); w the outer
+// weight [h] (null: none); residual f32 [num_rows, h] updated in place, or null with out32 f32 [num_rows, h];
+// cast [num_rows, h] act dtype or null.
+DINFER_API int dinfer_branch_norm(const void* a, const void* wa, const void* b, const void* wb, float coef,
+                                  float inner_eps, const void* w, float eps, float* residual, float* out32, void* cast,
+                                  int num_rows, int h, int act_dtype, int w_dtype, cudaStream_t stream) {
+  if (h <= 0 || num_rows < 0) return refuse(DINFER_BAD_ARGUMENT, "branch_norm: bad sizes rows=%d h=%d", num_rows, h);
+  if (!a || (b && (!wa || !wb)) || (!residual && !out32))
+    return refuse(DINFER_BAD_ARGUMENT, "branch_norm: a branch without its weight, or no output");
+  const size_t row_bytes = (size_t)h * sizeof(float);
+  if (row_bytes > 200 * 1024) return refuse(DINFER_BAD_ARGUMENT, "branch_norm: rows of %d above the limit", h);
+  if (num_rows == 0) return 0;
+  int threads = (h + 31) / 32 * 32;
+  if (threads > 1024) threads = 1024;
+  DINFER_DISPATCH_DTYPE(act_dtype, TA,
+    DINFER_DISPATCH_DTYPE(w_dtype, TW, {
+      if (row_bytes > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(branch_norm_kernel<TA, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)row_bytes);
+        if (e != cudaSuccess) return refuse((int)e, "branch_norm: shared memory opt-in failed: %s", cudaGetErrorString(e));
+      }
+      launch_pdl(branch_norm_kernel<TA, TW>, dim3(num_rows), dim3(threads), row_bytes, stream, (const TA*)a, (const TW*)wa,
+                 (const TA*)b, (const TW*)wb, coef, inner_eps, (const TW*)w, eps, residual, out32, (TA*)cast, h);
+      return cuda_status("branch_norm");
+    }));
+  return 0;
+}

@@ -400,3 +400,91 @@ DINFER_API int dinfer_qk_post(void* qkv, int64_t ld, const int* positions, const
   return dinfer_qk_post_styled(qkv, ld, positions, q_weight, k_weight, eps, cos_sin, rot, 0, cache, slots, block_size, T, H,
                                Hkv, D, act_dtype, w_dtype, stream);
 }
+
+// The general form, for mixers whose keys and values differ in width or whose head norm comes behind the rotation:
+// per (token, head) of q (H heads of D), k (Hkv of D) and v (Hkv of Dv), in one pass
+//   norm_first:  x <- rms(x) [* w];  x <- rot(x)          (the order of the kernel above)
+//   else:        x <- rot(x);        x <- rms(x) [* w]    (norm = 1; the weights may be null: a norm without a weight)
+// q and k written back in place; k and v to the token's slot of a cache [blocks, 2, Hkv, block_size, Dc], whose
+// rows are Dc = max(D, Dv) wide (k in the first D, v in the first Dv elements of a row).
+namespace {
+
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(WARPS * 32)
+qkv_post_general_kernel(TA* __restrict__ qkv, int64_t ld, const int* __restrict__ positions,
+                        const TW* __restrict__ q_weight, const TW* __restrict__ k_weight, int norm, int norm_first,
+                        float eps, const float* __restrict__ cos_sin, int rot, int interleaved, TA* __restrict__ cache,
+                        const int* __restrict__ slots, int block_size, int H, int Hkv, int D, int Dv, int Dc) {
+  __shared__ float sm[WARPS][MAX_D];
+  pdl_enter();
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.y * WARPS + warp;
+  if (head >= H + 2 * Hkv) return;
+  const int kind = head < H ? 0 : (head < H + Hkv ? 1 : 2);
+  const int width = kind == 2 ? Dv : D;
+  TA* x = qkv + (int64_t)t * ld + (kind == 2 ? (int64_t)(H + Hkv) * D + (int64_t)(head - H - Hkv) * Dv : (int64_t)head * D);
+  float* xs = sm[warp];
+  for (int e = lane; e < width; e += 32) xs[e] = to_f32<TA>(x[e]);
+  __syncwarp();
+  if (kind != 2) {
+    const TW* w = kind == 0 ? q_weight : k_weight;
+    auto normalize = [&]() {
+      float ss = 0.f;
+      for (int e = lane; e < D; e += 32) ss += xs[e] * xs[e];
+      ss = warp_sum(ss);
+      const float rinv = 1.f / sqrtf(ss / (float)D + eps);
+      for (int e = lane; e < D; e += 32) xs[e] = xs[e] * rinv * (w ? to_f32<TW>(w[e]) : 1.f);
+      __syncwarp();
+    };
+    if (norm && norm_first) normalize();
+    if (cos_sin) {
+      const float* cs = cos_sin + (int64_t)positions[t] * rot;
+      const int half = rot >> 1;
+      for (int i = lane; i < half; i += 32) {
+        const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
+        const float c = cs[i], s = cs[half + i];
+        const float u = xs[a], v = xs[b];
+        xs[a] = u * c - v * s;
+        xs[b] = v * c + u * s;
+      }
+      __syncwarp();
+    }
+    if (norm && !norm_first) normalize();
+    for (int e = lane; e < D; e += 32) x[e] = from_f32<TA>(xs[e]);
+  }
+  if (kind != 0 && cache) {
+    const int slot = slots[t];
+    if (slot < 0) return;
+    const int hk = kind == 1 ? head - H : head - H - Hkv;
+    const int64_t blk = slot / block_size, off = slot % block_size;
+    TA* dst = cache + (((blk * 2 + (kind == 2)) * Hkv + hk) * block_size + off) * Dc;
+    for (int e = lane; e < width; e += 32) dst[e] = from_f32<TA>(xs[e]);
+  }
+}
+
+}  // namespace
+
+DINFER_API int dinfer_qkv_post_general(void* qkv, int64_t ld, const int* positions, const void* q_weight,
+                                       const void* k_weight, int norm, int norm_first, float eps, const float* cos_sin,
+                                       int rot, int interleaved, void* cache, const int* slots, int block_size, int T,
+                                       int H, int Hkv, int D, int Dv, int Dc, int act_dtype, int w_dtype,
+                                       cudaStream_t stream) {
+  if (T < 0 || H <= 0 || Hkv < 0 || D <= 0 || Dv <= 0 || Dc < D || Dc < Dv)
+    return refuse(DINFER_BAD_ARGUMENT, "qkv_post_general: bad sizes T=%d H=%d Hkv=%d D=%d Dv=%d Dc=%d", T, H, Hkv, D, Dv, Dc);
+  if (D > MAX_D || Dv > MAX_D) return refuse(DINFER_BAD_ARGUMENT, "qkv_post_general: head sizes %d / %d above the limit %d", D, Dv, MAX_D);
+  if (cos_sin && (rot <= 0 || rot > D || (rot & 1)))
+    return refuse(DINFER_BAD_ARGUMENT, "qkv_post_general: rotary dim %d must be even and at most head_dim %d", rot, D);
+  if (ld < (int64_t)(H + Hkv) * D + (int64_t)Hkv * Dv) return refuse(DINFER_BAD_ARGUMENT, "qkv_post_general: row stride below the row's width");
+  if (cache && block_size <= 0) return refuse(DINFER_BAD_ARGUMENT, "qkv_post_general: block_size %d", block_size);
+  if (T == 0) return 0;
+  dim3 grid(T, (H + 2 * Hkv + WARPS - 1) / WARPS);
+  DINFER_DISPATCH_DTYPE(act_dtype, TA,
+    DINFER_DISPATCH_DTYPE(w_dtype, TW, {
+      launch_pdl(qkv_post_general_kernel<TA, TW>, grid, dim3(WARPS * 32), 0, stream, (TA*)qkv, ld, positions,
+                 (const TW*)q_weight, (const TW*)k_weight, norm, norm_first, eps, cos_sin, rot, interleaved, (TA*)cache,
+                 slots, block_size, H, Hkv, D, Dv, Dc);
+      return cuda_status("qkv_post_general");
+    }));
+  return 0;
+}

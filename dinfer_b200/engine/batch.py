@@ -182,7 +182,7 @@ class PlanBuilder:
         if table_width is not None:
             width = table_width
         else:
-            small = min(m.block_sizes)                       # one width for all groups: what the smallest pages need
+            small = min(m.block_sizes or [m.block_size])     # one width for all groups: what the smallest pages need
             width = max(1, max((int(s_) + small - 1) // small for s_ in seq)) if B else 1
         if width > self.max_blocks:
             raise ValueError(f"a request needs {width} pages, the plan buffers hold {self.max_blocks}")

@@ -29,7 +29,7 @@ from ..config.model_config import read_config_json
 from ..config.registry import resolve_architecture
 from ..kernels import lib as kernel_lib
 from ..models.decoder import DecoderModel
-from ..parts.base import BuildEnv, CacheBinding, KvCacheNeed, StateNeed
+from ..parts.base import BuildEnv, CacheBinding, KvCacheNeed, StateNeed, split_needs
 from ..weights.loader import SafetensorsSource, WeightSource, load_tensors
 from .batch import DecodePlan, OutOfPages, PlanBuilder, StepEntry
 
@@ -166,7 +166,10 @@ class ModelRunner:
     def _make_caches(self) -> None:
         e = self.engine
         bs = e.block_size
-        needs = self.model.cache_needs()
+        # per schedule entry: (paged cache or None, fixed-size state or None); a mixer may keep one of each
+        both = [split_needs(n) for n in self.model.cache_needs()]
+        needs = [kv for kv, _ in both]
+        states = [st for _, st in both]
         group_keys: List[Any] = []
         entry_group: List[int] = []
         for n in needs:
@@ -202,7 +205,7 @@ class ModelRunner:
         self.num_blocks = int(num_blocks)
         group_blocks = [max(1, self.num_blocks * bs // b) for b in sizes]
         prefix = bool(e.enable_prefix_caching)
-        if prefix and (any(g.window is not None for g in groups) or any(isinstance(n, StateNeed) for n in needs)):
+        if prefix and (any(g.window is not None for g in groups) or any(st is not None for st in states)):
             raise ValueError("enable_prefix_caching: this model has windowed layers or per-request state, "
                              "whose cache cannot be shared between requests")
         if e.native_host:
@@ -211,21 +214,21 @@ class ModelRunner:
             Manager = CacheManager
         self.manager = Manager(groups, bs, group_blocks, e.max_num_seqs, enable_prefix_caching=prefix)
         self.bindings: List[CacheBinding] = []
-        for i, (entry, n) in enumerate(zip(self.spec.schedule, needs)):
+        for i, (entry, n, sn) in enumerate(zip(self.spec.schedule, needs, states)):
             if entry.cache_from is not None:
                 src = self.bindings[entry.cache_from]
                 self.bindings.append(CacheBinding(kv=src.kv, group=src.group, write=False, state=src.state))
-            elif isinstance(n, KvCacheNeed):
+                continue
+            binding = CacheBinding()
+            if isinstance(n, KvCacheNeed):
                 g = entry_group[i]
-                kv = torch.zeros((group_blocks[g], n.planes, n.num_kv_heads, sizes[g], n.head_dim),
-                                 dtype=self.act_dtype, device=self.device)
-                self.bindings.append(CacheBinding(kv=kv, group=entry_group[i], write=True))
-            elif isinstance(n, StateNeed):
+                binding.kv = torch.zeros((group_blocks[g], n.planes, n.num_kv_heads, sizes[g], n.head_dim),
+                                         dtype=self.act_dtype, device=self.device)
+                binding.group = g
+            if isinstance(sn, StateNeed):
                 # one slot more than requests: the rows that pad a captured batch point at it
-                st = torch.zeros((e.max_num_seqs + 1,) + tuple(n.shape), dtype=n.dtype, device=self.device)
-                self.bindings.append(CacheBinding(state=st, group=-1, write=True))
-            else:
-                self.bindings.append(CacheBinding())
+                binding.state = torch.zeros((e.max_num_seqs + 1,) + tuple(sn.shape), dtype=sn.dtype, device=self.device)
+            self.bindings.append(binding)
 
     # ---- one step
     def step(self, entries: Sequence[StepEntry], placeholders: bool = False) -> torch.Tensor:
@@ -300,7 +303,7 @@ class ModelRunner:
         dev = torch.empty(self.plan.words(bucket, bucket, bucket, width), dtype=torch.int32, device=self.device)
         ids, rows, ctx = self.plan.build([], [], pad_reqs=bucket, table_width=width, dev=dev)
         # the split count is part of the captured launch: fixed per bucket, for the longest context
-        hkv = max([n.num_kv_heads for n in self.model.cache_needs() if isinstance(n, KvCacheNeed)] or [1])
+        hkv = max([kv.num_kv_heads for kv, _ in map(split_needs, self.model.cache_needs()) if kv is not None] or [1])
         ctx.decode_splits = attention_ops.decode_splits(bucket, hkv, self.engine.max_model_len)
         ctx.split_norms = self.engine.split_norms is True
         ctx.prev_tokens = self.sampled
@@ -431,7 +434,7 @@ class ModelRunner:
         # hold them without passing the longest request the tables and the position table are made for
         places = capture_places(total, n_places, bucket, self.engine.max_model_len)
         ids, rows, ctx = self.plan.build([], [], table_width=width, dev=dev, slots=places)
-        hkv = max([n.num_kv_heads for n in self.model.cache_needs() if isinstance(n, KvCacheNeed)] or [1])
+        hkv = max([kv.num_kv_heads for kv, _ in map(split_needs, self.model.cache_needs()) if kv is not None] or [1])
         ctx.decode_splits = attention_ops.decode_splits(max(1, bucket), hkv, self.engine.max_model_len)
         ctx.max_seq_len = self.engine.max_model_len
         ctx.max_prefill_seq_len = min(self.SHORT_CONTEXT, self.engine.max_model_len) if short else self.engine.max_model_len

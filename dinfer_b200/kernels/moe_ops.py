@@ -34,6 +34,24 @@ def route(logits: torch.Tensor, num_experts: int, top_k: int, scoring: str = "so
     return ids, weights, gate
 
 
+def route_table(tokens: torch.Tensor, table: torch.Tensor, num_experts: int,
+                prev: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Routing without a router: ``table`` [vocab, top] int32 names each token id's experts, every choice weighs
+    ``1 / top``.  ``tokens`` int32 [T]; an id -(r + 1) stands for ``prev[r]``.  Returns (ids int32 [T, top], weights f32)."""
+    require_cuda(tokens, table, prev)
+    if tokens.dtype != torch.int32 or table.dtype != torch.int32 or table.dim() != 2 or not table.is_contiguous() \
+            or not tokens.is_contiguous():
+        raise KernelError("moe route_table: tokens int32 [T], table int32 [vocab, top], contiguous")
+    T, top = tokens.numel(), table.shape[1]
+    ids = torch.empty((T, top), dtype=torch.int32, device=tokens.device)
+    weights = torch.empty((T, top), dtype=torch.float32, device=tokens.device)
+    lib, f = _fn("moe", "dinfer_moe_route_table",
+                 [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    check(lib, f(ptr(tokens), ptr(prev), prev.numel() if prev is not None else 0, ptr(table), table.shape[0], ptr(ids),
+                 ptr(weights), T, num_experts, top, stream_handle()), "moe_route_table")
+    return ids, weights
+
+
 def router(h: torch.Tensor, w_router: torch.Tensor, top_k: int, scoring: str = "softmax", renormalize: bool = False,
            w_gate: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
     """The router from its input: logits by the 32-bit product (``w_router`` [E, K], and ``w_gate`` [K] as one more

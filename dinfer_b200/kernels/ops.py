@@ -196,14 +196,19 @@ def qk_post(qkv: torch.Tensor, positions: torch.Tensor, num_heads: int, num_kv_h
 
 def attention_generic(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                       cu_seqlens: torch.Tensor, positions: torch.Tensor, num_heads: int, num_kv_heads: int,
-                      head_dim: int, scale: float, window: int = 0) -> torch.Tensor:
+                      head_dim: int, scale: float, window: int = 0, v_dim: Optional[int] = None,
+                      sink: bool = False) -> torch.Tensor:
     """Paged causal attention, plain arithmetic, any head size.  ``q`` may be a strided view (for
-    instance the q columns of the qkv rows)."""
+    instance the q columns of the qkv rows).  ``v_dim``: the values' width where it differs from the keys' (the
+    cache's rows are then ``max(head_dim, v_dim)`` wide, ``out`` holds head h at ``h * v_dim``); ``sink``: one more
+    term of score 0 and no value in the softmax's denominator."""
     require_cuda(q, out, cache, block_table, cu_seqlens, positions)
     _rows_contiguous(q, "attention q")
     _rows_contiguous(out, "attention out")
     T = q.shape[0]
     B = cu_seqlens.numel() - 1
+    v_dim = head_dim if v_dim is None else int(v_dim)
+    row = max(head_dim, v_dim)
     if q.dtype != cache.dtype or out.dtype != q.dtype:
         raise KernelError("attention: q, out and cache must have one dtype")
     for t, n in ((block_table, "block_table"), (cu_seqlens, "cu_seqlens"), (positions, "positions")):
@@ -211,17 +216,81 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, b
             raise KernelError(f"attention: {n} must be contiguous int32")
     if block_table.dim() != 2 or block_table.shape[0] < B or positions.numel() != T:
         raise KernelError("attention: block_table [B, max_blocks], positions [T]")
-    if cache.dim() != 5 or cache.shape[1] != 2 or cache.shape[2] != num_kv_heads or cache.shape[4] != head_dim \
+    if cache.dim() != 5 or cache.shape[1] != 2 or cache.shape[2] != num_kv_heads or cache.shape[4] != row \
             or not cache.is_contiguous():
-        raise KernelError(f"attention: cache shape {tuple(cache.shape)} is not [blocks, 2, Hkv, block, D]")
-    lib, f = _fn("attention_generic", "dinfer_attention_generic",
+        raise KernelError(f"attention: cache shape {tuple(cache.shape)} is not [blocks, 2, Hkv, block, {row}]")
+    lib, f = _fn("attention_generic", "dinfer_attention_generic_ex",
                  [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                  c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p])
+                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p])
     check(lib, f(ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(cache), ptr(block_table),
                  block_table.shape[1], ptr(cu_seqlens), ptr(positions), T, B, num_heads, num_kv_heads,
-                 head_dim, cache.shape[3], float(scale), int(window), dtype_code(q.dtype), stream_handle()),
-          "attention_generic")
+                 head_dim, v_dim, row, cache.shape[3], float(scale), int(window), int(bool(sink)),
+                 dtype_code(q.dtype), stream_handle()), "attention_generic")
     return out
+
+
+def qkv_post_general(qkv: torch.Tensor, positions: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
+                     v_dim: int, eps: float, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
+                     norm: bool, norm_first: bool, cos_sin: Optional[torch.Tensor], cache: Optional[torch.Tensor],
+                     slots: Optional[torch.Tensor], block_size: int, interleaved: bool = False) -> None:
+    """The general q/k/v post-processing: per-head RMS norm of q and k (``norm``; the weights may be None: a norm
+    without a weight) before or behind (``norm_first``) the rotation, q and k written back in place, k and v (v of
+    width ``v_dim``) into a paged cache whose rows are ``max(head_dim, v_dim)`` wide."""
+    require_cuda(qkv, positions, q_weight, k_weight, cos_sin, cache, slots)
+    _rows_contiguous(qkv, "qkv_post_general")
+    T = qkv.shape[0]
+    row = max(head_dim, v_dim)
+    if positions.dtype != torch.int32 or positions.numel() != T:
+        raise KernelError("qkv_post_general: positions int32 [T]")
+    if (q_weight is None) != (k_weight is None):
+        raise KernelError("qkv_post_general: q and k norm weights come together")
+    w_dt = q_weight.dtype if q_weight is not None else torch.float32
+    if q_weight is not None and (q_weight.numel() != head_dim or k_weight.numel() != head_dim or k_weight.dtype != w_dt):
+        raise KernelError("qkv_post_general: norm weights must be [head_dim] of one dtype")
+    rot = 0
+    if cos_sin is not None:
+        if cos_sin.dtype != torch.float32 or not cos_sin.is_contiguous() or cos_sin.dim() != 2:
+            raise KernelError("qkv_post_general: angle table must be contiguous float32 [max_pos, rot]")
+        rot = cos_sin.shape[1]
+    if cache is not None:
+        if cache.dtype != qkv.dtype or not cache.is_contiguous() or slots is None or slots.dtype != torch.int32 \
+                or slots.numel() != T or tuple(cache.shape[1:]) != (2, num_kv_heads, block_size, row):
+            raise KernelError(f"qkv_post_general: cache [blocks, 2, {num_kv_heads}, {block_size}, {row}] of the "
+                              f"activations' dtype, contiguous; slots int32 [T]")
+    lib, f = _fn("qk_post", "dinfer_qkv_post_general",
+                 [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_int,
+                  c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    check(lib, f(ptr(qkv), qkv.stride(0), ptr(positions), ptr(q_weight), ptr(k_weight), int(bool(norm)),
+                 int(bool(norm_first)), float(eps), ptr(cos_sin), rot, int(bool(interleaved)), ptr(cache), ptr(slots),
+                 block_size, T, num_heads, num_kv_heads, head_dim, v_dim, row, dtype_code(qkv.dtype), dtype_code(w_dt),
+                 stream_handle()), "qkv_post_general")
+
+
+def branch_norm(a: torch.Tensor, weight: Optional[torch.Tensor], eps: float, residual: Optional[torch.Tensor] = None,
+                out32: Optional[torch.Tensor] = None, cast: Optional[torch.Tensor] = None,
+                inner=None, b: Optional[torch.Tensor] = None, coef: float = 1.0, inner_eps: float = 0.0):
+    """A branch output normed before it joins the residual stream: ``residual += rms(y) * weight`` (or ``out32 = ...``
+    without a residual; ``weight`` None: no outer norm), ``cast = T(residual)`` on the way.  ``y = a``, or with
+    ``inner = (w_a, w_b)``: ``y = coef * (rms(a) * w_a + rms(b) * w_b)`` (``b`` None: one branch).  32-bit throughout."""
+    require_cuda(a, b, weight, residual, out32, cast)
+    R, h = a.shape
+    wa, wb = inner if inner is not None else (None, None)
+    ws = [w for w in (weight, wa, wb) if w is not None]
+    w_dt = ws[0].dtype if ws else torch.float32
+    for w in ws:
+        _opt_vec(w, h, w_dt, "branch_norm: a weight")
+    if not a.is_contiguous() or (b is not None and (b.shape != a.shape or b.dtype != a.dtype or not b.is_contiguous())):
+        raise KernelError("branch_norm: branches [R, h] contiguous of one dtype")
+    for t, dt in ((residual, torch.float32), (out32, torch.float32), (cast, a.dtype)):
+        if t is not None and (tuple(t.shape) != (R, h) or t.dtype != dt or not t.is_contiguous()):
+            raise KernelError("branch_norm: residual / out32 f32 [R, h], cast [R, h] of the branches' dtype, contiguous")
+    lib, f = _fn("norm", "dinfer_branch_norm",
+                 [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_float, c_void_p, c_void_p,
+                  c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    check(lib, f(ptr(a), ptr(wa), ptr(b), ptr(wb), float(coef), float(inner_eps), ptr(weight), float(eps),
+                 ptr(residual), ptr(out32), ptr(cast), R, h, dtype_code(a.dtype), dtype_code(w_dt), stream_handle()),
+          "branch_norm")
+    return residual if residual is not None else out32
 
 
 def _opt_vec(t: Optional[torch.Tensor], h: int, dt: torch.dtype, what: str) -> None:

@@ -11,7 +11,8 @@ from typing import Dict, List, Optional
 import torch
 
 from ..kernels import ops
-from ..parts import attention, block, latent_attention, mlp, moe, norm, rope  # noqa: F401  (register the built-in parts)
+from ..parts import (attention, block, delta_rule, latent_attention, mlp, moe, norm, parallel_mixers,  # noqa: F401
+                     rope)                                # (register the built-in parts)
 from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, BuildEnv, CacheBinding, ResidualStream,
                           StepContext, build_part)
 from ..parts.linear import Linear
@@ -81,8 +82,8 @@ class DecoderModel:
     def graph_capturable(self) -> bool:
         """Whether a step of this model can be captured in a CUDA graph: every mixer that keeps per-request state
         must say so (``Mixer.graph_capturable``); mixers without state always can."""
-        from ..parts.base import StateNeed
-        return all(not isinstance(b.mixer.cache_need(), StateNeed) or bool(b.mixer.graph_capturable) for b in self.blocks)
+        from ..parts.base import split_needs
+        return all(split_needs(b.mixer.cache_need())[1] is None or bool(b.mixer.graph_capturable) for b in self.blocks)
 
     def can_split_norms(self, rows: int) -> bool:
         """Whether some norm of the model can be taken apart for steps of this many rows."""
@@ -103,12 +104,16 @@ class DecoderModel:
         T = ids.numel()
         x = torch.empty((T, s.hidden_size), dtype=torch.float32, device=ids.device)
         ops.embedding(ids, self.embedding, x, prev=ctx.prev_tokens, scale=s.embedding_scale)
+        ctx.token_ids = ids
         stream = ResidualStream(x)
         order = [self.blocks[e.layer] for e in s.schedule]
         for i, (block, binding) in enumerate(zip(order, bindings)):
             block.forward(stream, ctx, binding, next_block=order[i + 1] if i + 1 < len(order) else None)
         if logits_rows.numel() == 0:
             return torch.empty((0, s.vocab_size), dtype=torch.float32, device=ids.device)
+        if not isinstance(stream.pending, (torch.Tensor, type(None))):
+            from ..parts.base import resolve_pending
+            resolve_pending(stream)
         f = self.final_norm.forward(stream.x, delta=stream.pending, rows=logits_rows)
         logits = self.lm_head(f, out_dtype=torch.float32)
         if s.logit_softcap > 0:

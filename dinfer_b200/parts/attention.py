@@ -26,8 +26,11 @@ from .spec import PartSpec, TensorDecl
 class GQAttention(Mixer):
     """params: ``num_heads``, ``num_kv_heads``, ``head_dim``, ``qk_norm`` (bool), ``eps``,
     ``position`` (a PartSpec), optional ``window``, ``scale``, ``bias`` (bool: the four projections have a bias,
-    named like their weights with ``.bias``), and the tensor names ``q_proj``, ``k_proj``, ``v_proj``, ``o_proj``,
-    ``q_norm``, ``k_norm`` (after the prefix)."""
+    named like their weights with ``.bias``, or with ``bias_suffix`` added to the weight's name), and the tensor
+    names ``q_proj``, ``k_proj``, ``v_proj``, ``o_proj``, ``q_norm``, ``k_norm`` (after the prefix).  Further:
+    ``v_dim`` (the values' width where it differs from ``head_dim``), ``qk_norm_order`` ("before" the rotation, the
+    default, or "after" it), ``qk_norm_weight`` (False: the head norm has no weight), ``sink`` (the softmax has one
+    more term of score 0 that carries no value: ``p_j = exp(s_j) / (1 + sum exp(s_j))``)."""
 
     def __init__(self, params, env: BuildEnv, prefix=""):
         super().__init__(params, env, prefix)
@@ -44,6 +47,15 @@ class GQAttention(Mixer):
         self.page_size = p.get("cache_block_size")           # None: the engine's page size
         self.scale = float(p.get("scale", 1.0 / math.sqrt(self.D)))
         self.bias = bool(p.get("bias", False))
+        self.bias_suffix = p.get("bias_suffix")
+        self.Dv = int(p.get("v_dim", self.D))
+        self.sink = bool(p.get("sink", False))
+        self.norm_after = p.get("qk_norm_order", "before") == "after"
+        self.norm_weight = bool(p.get("qk_norm_weight", True))
+        if p.get("qk_norm_order", "before") not in ("before", "after") or self.Dv <= 0:
+            raise ValueError("attention: qk_norm_order is before or after, v_dim positive")
+        # the q/k kernel with lane paths takes the usual order and equal widths; anything else takes the general one
+        self.general = self.Dv != self.D or (self.qk_norm and (self.norm_after or not self.norm_weight))
         pos: PartSpec = p.get("position") or PartSpec("none")
         self.position = build_part(POSITION_ENCODINGS, pos, env, prefix)
         n = lambda key, default: prefix + p.get(key, default)
@@ -57,17 +69,19 @@ class GQAttention(Mixer):
         self.q_norm_w = self.k_norm_w = None
 
     def declare(self) -> List[TensorDecl]:
-        H, Hkv, D, h = self.H, self.Hkv, self.D, self.hidden
+        H, Hkv, D, Dv, h = self.H, self.Hkv, self.D, self.Dv, self.hidden
         d = [TensorDecl(self.names["q"], (H * D, h)), TensorDecl(self.names["k"], (Hkv * D, h)),
-             TensorDecl(self.names["v"], (Hkv * D, h)), TensorDecl(self.names["o"], (h, H * D))]
-        if self.qk_norm:
+             TensorDecl(self.names["v"], (Hkv * Dv, h)), TensorDecl(self.names["o"], (h, H * Dv))]
+        if self.qk_norm and self.norm_weight:
             d += [TensorDecl(self.names["qn"], (D,), init="ones"), TensorDecl(self.names["kn"], (D,), init="ones")]
         if self.bias:
-            d += [TensorDecl(self._bias_name(x), (n,)) for x, n in (("q", H * D), ("k", Hkv * D), ("v", Hkv * D), ("o", h))]
+            d += [TensorDecl(self._bias_name(x), (n,)) for x, n in (("q", H * D), ("k", Hkv * D), ("v", Hkv * Dv), ("o", h))]
         return d
 
     def _bias_name(self, which: str) -> str:
         name = self.names[which]
+        if self.bias_suffix:
+            return name + self.bias_suffix
         return (name[:-len(".weight")] if name.endswith(".weight") else name) + ".bias"
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
@@ -80,16 +94,20 @@ class GQAttention(Mixer):
             o_bias = tensors[self._bias_name("o")]
         self.qkv = Linear(torch.cat([q.to(dt), k.to(dt), v.to(dt)], dim=0), qkv_bias)
         self.o = Linear(tensors[self.names["o"]], o_bias)
-        if self.qk_norm:
+        if self.qk_norm and self.norm_weight:
             self.q_norm_w = tensors[self.names["qn"]].contiguous()
             self.k_norm_w = tensors[self.names["kn"]].to(self.q_norm_w.dtype).contiguous()
 
     def cache_need(self):
-        return KvCacheNeed(self.Hkv, self.D, self.window, int(self.page_size) if self.page_size else None)
+        return KvCacheNeed(self.Hkv, max(self.D, self.Dv), self.window, int(self.page_size) if self.page_size else None)
+
+    def _fast(self, dtype) -> bool:
+        """Whether the tensor-core kernels take this attention: keys and values of one width, no sink."""
+        return self.Dv == self.D and not self.sink and attention_ops.tc_supported(dtype, self.D, self.H // self.Hkv)
 
     def kernel_libraries(self):
         att = ["attention_generic"]
-        if attention_ops.tc_supported(self.env.act_dtype, self.D, self.H // self.Hkv):
+        if self._fast(self.env.act_dtype):
             att = ["attention_tc"]
             if self.D in (64, 128):
                 att += ["attention_decode", "attention_umma", "attention_umma64"]
@@ -107,7 +125,14 @@ class GQAttention(Mixer):
         qkv = self.qkv(x)
         kv = cache.kv if cache.write else None
         table = self.position.fused_table()
-        if self.position.fused:
+        if self.general:
+            if not self.position.fused:
+                raise NotImplementedError("attention: a head norm behind the rotation, or values of another width, "
+                                          "need a position encoding the q/k kernel applies")
+            ops.qkv_post_general(qkv, ctx.positions, H, Hkv, D, self.Dv, self.eps, self.q_norm_w, self.k_norm_w,
+                                 self.qk_norm, not self.norm_after, table, kv, g.slot_mapping, g.block_size,
+                                 interleaved=getattr(self.position, "interleaved", False))
+        elif self.position.fused:
             ops.qk_post(qkv, ctx.positions, H, Hkv, D, self.eps, self.q_norm_w, self.k_norm_w, table,
                         kv, g.slot_mapping, g.block_size, interleaved=getattr(self.position, "interleaved", False))
         else:
@@ -120,7 +145,7 @@ class GQAttention(Mixer):
             if kv is not None:
                 ops.qk_post(qkv, ctx.positions, H, Hkv, D, self.eps, None, None, None, kv,
                             g.slot_mapping, g.block_size)
-        out = torch.empty((qkv.shape[0], H * D), dtype=qkv.dtype, device=qkv.device)
+        out = torch.empty((qkv.shape[0], H * self.Dv), dtype=qkv.dtype, device=qkv.device)
         self.attend(qkv[:, :H * D], out, cache.kv, g, ctx)
         if sink is not None:                               # (residual, the norm behind this mixer)
             return self.o.into_residual(out, sink[0], sink[1])
@@ -130,7 +155,7 @@ class GQAttention(Mixer):
         """Tensor-core kernels where they take the head size (bfloat16; 32, 64, 128), else the
         plain-arithmetic kernel, which takes every size."""
         window = int(self.window or 0)
-        if attention_ops.tc_supported(q.dtype, self.D, self.H // self.Hkv):
+        if self._fast(q.dtype):
             splits = ctx.decode_splits or attention_ops.decode_splits(ctx.num_reqs, self.Hkv, ctx.max_seq_len)
             tc_decode = ctx.any_decode
             if ctx.any_decode and attention_ops.decode_supported(q.dtype, self.D, self.H // self.Hkv, g.block_size):
@@ -164,4 +189,4 @@ class GQAttention(Mixer):
                                            tc_prefill, splits)
         else:
             ops.attention_generic(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.positions, self.H, self.Hkv,
-                                  self.D, self.scale, window)
+                                  self.D, self.scale, window, v_dim=self.Dv, sink=self.sink)

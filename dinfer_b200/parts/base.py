@@ -78,6 +78,7 @@ class StepContext:
                                        # take max_seq_len); inside a captured graph a bound for all its replays
     split_norms: bool = False          # norms between two products may be taken apart (see HalfNormed)
     prev_tokens: Optional[torch.Tensor] = None   # int32 [rows]: a token id -(r + 1) stands for prev_tokens[r]
+    token_ids: Optional[torch.Tensor] = None     # int32 [T]: the step's token ids, for parts that look a token up in a table
     # host copies for parts written in plain torch (tests, toy parts)
     cu_seqlens_host: Sequence[int] = ()
     seq_lens_host: Sequence[int] = ()
@@ -157,10 +158,22 @@ class Mixer(Part):
     graph_capturable = False
 
     def cache_need(self):
+        """None, a ``KvCacheNeed``, a ``StateNeed``, or a list with one of each (a mixer made of several: its binding
+        then carries both ``kv`` and ``state``)."""
         return None
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
         raise NotImplementedError
+
+
+def split_needs(need):
+    """(KvCacheNeed | None, StateNeed | None) of what ``Mixer.cache_need`` returned."""
+    items = list(need) if isinstance(need, (list, tuple)) else [need]
+    kv = [n for n in items if isinstance(n, KvCacheNeed)]
+    st = [n for n in items if isinstance(n, StateNeed)]
+    if len(kv) > 1 or len(st) > 1 or len(kv) + len(st) != len([n for n in items if n is not None]):
+        raise ValueError("a mixer keeps at most one paged cache and one fixed-size state")
+    return (kv[0] if kv else None), (st[0] if st else None)
 
 
 class FeedForward(Part):
@@ -205,14 +218,34 @@ def resolve_pending(stream: "ResidualStream") -> None:
 
 
 @dataclass
+class NormedBranches:
+    """The output of mixers that run side by side, not yet put together: ``coef * sum_i rms(tensor_i) * weight_i``,
+    each branch divided by its own root mean square (``eps`` inside the root) over the model width.  An arrangement
+    whose next kernel can do that sum takes it as it is; any other consumer calls ``resolve``."""
+    items: List[Tuple[torch.Tensor, torch.Tensor]]
+    coef: float
+    eps: float
+
+    def resolve(self) -> torch.Tensor:
+        """The sum as a 32-bit tensor [T, h]."""
+        from ..kernels import ops
+        a, wa = self.items[0]
+        b, wb = self.items[1] if len(self.items) > 1 else (None, None)
+        out = torch.empty(a.shape, dtype=torch.float32, device=a.device)
+        return ops.branch_norm(a, None, 0.0, out32=out, inner=(wa, wb), b=b, coef=self.coef, inner_eps=self.eps)
+
+
+@dataclass
 class ResidualStream:
     """The 32-bit residual ``x`` and either a part's output that has not been added to it yet (``pending``) or
     the input of the next block's mixer, already added and half normed by the part before (``half``, made for
-    the norm ``half_norm``)."""
+    the norm ``half_norm``).  ``cast``: ``x`` in the activation type, where the kernel that last changed ``x`` wrote
+    it on the way (for arrangements whose sublayers read the stream itself)."""
     x: torch.Tensor
     pending: Optional[torch.Tensor] = None
     half: Optional["HalfNormed"] = None
     half_norm: Optional["Norm"] = None
+    cast: Optional[torch.Tensor] = None
 
 
 class Block:

@@ -4,6 +4,8 @@ from __future__ import annotations
 from typing import Optional
 
 from .base import BLOCKS, Block, CacheBinding, ResidualStream, StepContext
+import torch
+
 from .norm import RMSNorm
 
 
@@ -113,3 +115,61 @@ class ParallelResidual(Block):
         if h2 is not None:
             items.append((self.feed_forward.forward(h2, ctx), self.feed_forward_scale))
         stream.pending = ScaledDeltas(items)
+
+
+@BLOCKS.register("postnorm_residual")
+class PostNormResidual(Block):
+    """``x += norm1(mixer(x)); x += norm2(ffn(x))``: the norm sits on the sublayer's output only, the sublayers read
+    the stream itself (rounded to the activation type).
+
+    One kernel per sublayer does the norm, the add into the 32-bit stream and the rounded copy of the new stream
+    that the next sublayer's product reads (``ResidualStream.cast``).  A mixer that hands over branches which are
+    each normed first and then averaged (``NormedBranches``) has that done in the same kernel.  A layer may have no
+    feed-forward (kind "none")."""
+
+    def kernel_libraries(self):
+        return ["norm", "elementwise"]
+
+    def _input(self, stream: ResidualStream):
+        from ..kernels import ops
+        if self.env.act_dtype == torch.float32:
+            return stream.x
+        if stream.cast is None:
+            stream.cast = ops.cast(stream.x, torch.empty(stream.x.shape, dtype=self.env.act_dtype, device=stream.x.device))
+        return stream.cast
+
+    def _join(self, stream: ResidualStream, branch, norm) -> None:
+        from ..kernels import ops
+        from .base import NormedBranches
+        cast = None
+        if self.env.act_dtype != torch.float32:
+            cast = torch.empty(stream.x.shape, dtype=self.env.act_dtype, device=stream.x.device)
+        if isinstance(branch, NormedBranches):
+            (a, wa), (b, wb) = branch.items if len(branch.items) == 2 else (branch.items[0], (None, None))
+            ops.branch_norm(a, norm.weight, norm.eps, residual=stream.x, cast=cast, inner=(wa, wb), b=b,
+                            coef=branch.coef, inner_eps=branch.eps)
+        else:
+            ops.branch_norm(branch, norm.weight, norm.eps, residual=stream.x, cast=cast)
+        stream.cast = cast
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, cache: CacheBinding,
+                next_block: Optional[Block] = None) -> None:
+        from .base import resolve_pending
+        if stream.half is not None:
+            raise RuntimeError("a post-norm block does not take half-normed rows")
+        if stream.pending is not None:                     # a block of another arrangement ran before this one
+            from ..kernels import ops
+            if isinstance(stream.pending, torch.Tensor):
+                ops.scaled_add(stream.x, [(stream.pending, None)])
+                stream.pending = None
+            else:
+                resolve_pending(stream)
+            stream.cast = None
+        for part, norm in ((self.mixer, self.mixer_norm), (self.feed_forward, self.feed_forward_norm)):
+            if getattr(part, "absent", False):
+                continue
+            if not isinstance(norm, RMSNorm):
+                raise TypeError("postnorm_residual: the norms are RMS norms")
+            h = self._input(stream)
+            branch = part.forward(h, ctx, cache) if part is self.mixer else part.forward(h, ctx)
+            self._join(stream, branch, norm)

@@ -12,7 +12,8 @@ from .spec import TensorDecl
 
 @NORMS.register("rmsnorm")
 class RMSNorm(Norm):
-    """params: ``size``, ``eps``, ``weight`` (tensor name after the prefix).
+    """params: ``size``, ``eps``, ``weight`` (tensor name after the prefix), ``optional`` (the weight may be absent
+    from the file: the norm of a branch the layer does not have).
 
     ``out = T(v * rsqrt(mean(v^2) + eps) * w)`` with ``v = residual (+ delta)`` in 32-bit
     (crates/kernels/cuda/norm.cu:54-115, crates/layers/src/nn.rs:78-111)."""
@@ -22,13 +23,15 @@ class RMSNorm(Norm):
         self.size = int(params["size"])
         self.eps = float(params["eps"])
         self.weight_name = prefix + params.get("weight", "weight")
+        self.optional = bool(params.get("optional", False))
         self.weight: Optional[torch.Tensor] = None
 
     def declare(self) -> List[TensorDecl]:
-        return [TensorDecl(self.weight_name, (self.size,), init="ones")]
+        return [TensorDecl(self.weight_name, (self.size,), init="ones", optional=self.optional)]
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.weight = tensors[self.weight_name].contiguous()
+        w = tensors.get(self.weight_name) if self.optional else tensors[self.weight_name]
+        self.weight = None if w is None else w.contiguous()
 
     def kernel_libraries(self):
         return ["norm"]

@@ -75,12 +75,15 @@ class ModelSpec:
 
 @dataclass(frozen=True)
 class TensorDecl:
-    """A tensor a part takes from the weight file."""
+    """A tensor a part takes from the weight file.  A dimension of -1 is one the file decides (a rank that no key of
+    the configuration names); the part checks in ``bind`` that such dimensions agree with one another."""
     name: str
     shape: Tuple[int, ...]
     # "float": kept in bfloat16 (a tensor the file stores in 32-bit stays so; everything is
     # 32-bit in the float32 engine).  "int": an integer table, kept as int32.
     kind: str = "float"
     optional: bool = False
-    # how the random-weights mode fills it: "normal" (N(0, std)) or "ones" (1 + U(-jitter, jitter))
+    # how the random-weights mode fills it: "normal" (N(0, std)), "ones" (1 + U(-jitter, jitter)) or, for an integer
+    # table, "choices": every row holds different values out of range(init_arg)
     init: str = "normal"
+    init_arg: int = 0

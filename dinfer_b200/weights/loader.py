@@ -121,7 +121,7 @@ def verify(source: WeightSource, decls: Sequence[TensorDecl], allow_unexpected: 
                 missing.append(name)
             continue
         got = tuple(source.shape(name))
-        if got != tuple(d.shape):
+        if len(got) != len(d.shape) or any(w != -1 and w != g for g, w in zip(got, d.shape)):
             wrong_shape.append((name, got, tuple(d.shape)))
         dt = source.dtype(name)
         if d.kind == "float" and dt not in _FLOATS:

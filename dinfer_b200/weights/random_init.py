@@ -32,8 +32,14 @@ def random_tensor(decl: TensorDecl, seed: int, std: float, jitter: float, dtype:
                   device="cpu") -> torch.Tensor:
     gen = torch.Generator(device=device)
     gen.manual_seed(_tensor_seed(seed, decl.name))
+    if any(n < 0 for n in decl.shape):
+        raise ValueError(f"{decl.name}: a dimension the file decides has no size to draw (name it in the configuration)")
     if decl.kind == "int":
-        raise ValueError(f"{decl.name}: integer tables have no random rule")
+        if decl.init != "choices" or len(decl.shape) != 2 or not (0 < decl.shape[1] <= decl.init_arg):
+            raise ValueError(f"{decl.name}: integer tables have no random rule")
+        # every row: the first shape[1] entries of a random order of range(init_arg)
+        keys = torch.rand((decl.shape[0], decl.init_arg), generator=gen, device=device)
+        return keys.argsort(dim=1)[:, :decl.shape[1]].to(torch.int32)
     if decl.init == "ones":
         t = torch.rand(decl.shape, generator=gen, device=device, dtype=torch.float32)
         t = 1.0 + (2.0 * t - 1.0) * jitter
@@ -90,7 +96,7 @@ class RandomSource(WeightSource):
         return tuple(self.decls[name].shape)
 
     def dtype(self, name):
-        return self.dt
+        return torch.int32 if self.decls[name].kind == "int" else self.dt
 
     def get(self, name):
         return random_tensor(self.decls[name], self.seed, self.std, self.jitter, self.dt, self.device)
