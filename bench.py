@@ -358,6 +358,29 @@ DESIGN_SIZES = {
 }
 
 
+# ---------------------------------------------------------------- Zasipel beside Qwen3 at equal layer sizes
+def _zasipel_cfg(width, heads, kv_heads, dim, window, delta_heads, delta_kv, experts, top, ff, shared, vocab=32768):
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": window},
+            "rot": {"base": 10000.0, "dims": dim // 2}}
+    right = {"heads": delta_heads, "kv_heads": delta_kv, "dim": dim, "vdim": dim, "conv": 4}
+    channel = dict(right, kv_heads=delta_heads, decay_rank=dim // 2, gate_rank=dim // 2)
+    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}, "shared": {"ff": shared}}
+    par = {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": moe}
+    return {"architecture": "Zasipel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "layers": [par, par, {"type": "channel_delta", "mixer": channel, "mlp": moe}, par]}
+
+
+# four layers (three with attention over a window beside a delta rule, one with the per-channel delta rule alone), heads
+# of 64 or 128, a window of 1024, 16 or 64 experts of which a token uses 2 or 6, a shared expert; beside each the dense
+# Qwen3 layers of the same width and head count whose feed-forward has about the weights a Zasipel token uses
+ZASIPEL_SIZES = {
+    "small": (_zasipel_cfg(1024, 16, 4, 64, 1024, 16, 8, 16, 2, 512, 1024), _qwen3_cfg(1024, 16, 4, 64, 2048)),
+    "medium": (_zasipel_cfg(2048, 16, 4, 128, 1024, 16, 8, 64, 6, 1408, 2816), _qwen3_cfg(2048, 16, 4, 128, 7680)),
+    "large": (_zasipel_cfg(4096, 32, 8, 128, 1024, 32, 16, 64, 6, 2048, 4096), _qwen3_cfg(4096, 32, 8, 128, 12288)),
+}
+DESIGNS = {"dobedra": DESIGN_SIZES, "zasipel": ZASIPEL_SIZES}
+
+
 def _time_model(cfg, batch, context, prefill_tokens, steps, seed=5, profile=None):
     """(prefill ms of one prompt, decode ms per step of ``batch`` requests at ``context``, launches per decode step) of
     four layers of ``cfg`` with random weights: the prompt through the step function (best of three), the decode
@@ -417,15 +440,16 @@ def _time_model(cfg, batch, context, prefill_tokens, steps, seed=5, profile=None
 
 
 def design_run(a) -> int:
-    """``--design dobedra``: prefill and decode throughput of four Dobedra layers beside four Qwen3 layers of the same
-    width and head count, at the sizes of ``DESIGN_SIZES``; one JSON line."""
+    """``--design dobedra|zasipel``: prefill and decode throughput of four layers of the design beside four Qwen3 layers
+    of the same width and head count, at the sizes of ``DESIGNS``; one JSON line."""
     rows = {}
-    sizes = [a.design_size] if a.design_size else list(DESIGN_SIZES)
+    table = DESIGNS[a.design]
+    sizes = [a.design_size] if a.design_size else list(table)
     for name in sizes:
-        ours, theirs = DESIGN_SIZES[name]
+        ours, theirs = table[name]
         row = {}
-        for label, cfg in (("dobedra", ours), ("qwen3", theirs)):
-            if a.profile and label != (a.design_model or "dobedra"):
+        for label, cfg in ((a.design, ours), ("qwen3", theirs)):
+            if a.profile and label != (a.design_model or a.design):
                 continue
             pre, dec, launches = _time_model(cfg, a.batch, a.context, PREFILL_TOKENS, a.steps, profile=a.profile)
             row[label] = {"prefill_ms": round(pre, 3), "prefill_tok_s": round(PREFILL_TOKENS * 1e3 / pre, 1),
@@ -434,7 +458,7 @@ def design_run(a) -> int:
         rows[name] = row
     if a.profile:
         return 0
-    print(json.dumps({"metric": "Dobedra beside Qwen3, four layers at equal width and heads (bf16, random weights): "
+    print(json.dumps({"metric": f"{a.design.capitalize()} beside Qwen3, four layers at equal width and heads (bf16, random weights): "
                                 f"prefill of {PREFILL_TOKENS} tokens, decode at batch {a.batch} context {a.context}",
                       "sizes": rows, "steps": a.steps, "impl": "ours", "data": "synthetic"}))
     return 0
@@ -459,11 +483,11 @@ def main() -> int:
     ap.add_argument("--closed-loop", default=None, metavar="C,P,O",
                     help="the reference's serving measurement at engine level instead: C clients, each sending its "
                          "next request when the last has ended, prompts of P tokens, O generated tokens (--shape applies)")
-    ap.add_argument("--design", choices=["dobedra"], default=None,
+    ap.add_argument("--design", choices=["dobedra", "zasipel"], default=None,
                     help="instead of the benchmark: four layers of this design beside four Qwen3 layers of equal width, "
                          "prefill and decode, at a few layer sizes")
     ap.add_argument("--design-size", choices=["small", "medium", "large"], default=None, help="only this size")
-    ap.add_argument("--design-model", choices=["dobedra", "qwen3"], default=None, help="with --profile: which of the two")
+    ap.add_argument("--design-model", choices=["dobedra", "zasipel", "qwen3"], default=None, help="with --profile: which of the two")
     a = ap.parse_args()
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

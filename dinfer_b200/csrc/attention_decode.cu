@@ -38,6 +38,7 @@ struct Params {
   const int* block_table; int max_blocks;
   const int* cu_seqlens; const int* seq_lens;
   int H, Hkv, group, block_size, bs_log2, window;
+  int sink;          // one more softmax term of score 0 without a value (the TMA variant)
   float scale_log2;
   int splits;
   float* part_o;     // [B, H, splits, D]
@@ -677,6 +678,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const Pa
         acc += sm_o[(w * NHEADS + head) * D + d] * f;
       }
       if (!clustered) {
+        if (p.sink) L += exp2f(-M);                           // the sink: exp(0 - m), in the denominator only
         p.out[(int64_t)t0 * p.ldo + (int64_t)(hk * p.group + head) * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
       } else {
         const int owner = idx / share;
@@ -715,6 +717,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const Pa
         L += recv_ml[(sp * p.group + head) * 2 + 1] * f;
         acc += recv[sp * share + i] * f;
       }
+      if (p.sink) L += exp2f(-M);
       p.out[(int64_t)t0 * p.ldo + (int64_t)(hk * p.group + head) * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
     }
   }
@@ -835,7 +838,7 @@ DINFER_API int dinfer_attention_decode(const void* q, int64_t ldq, void* out, in
   p.cu_seqlens = cu_seqlens; p.seq_lens = seq_lens; p.H = H; p.Hkv = Hkv; p.group = H / Hkv;
   p.block_size = block_size; p.bs_log2 = 0;
   while ((1 << p.bs_log2) < block_size) ++p.bs_log2;
-  p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.splits = splits;
+  p.window = window; p.sink = 0; p.scale_log2 = scale * 1.4426950408889634f; p.splits = splits;
   p.part_o = scratch_floats;
   p.part_ml = scratch_floats ? scratch_floats + (int64_t)B * H * splits * D : nullptr;
   p.counters = scratch_counters; p.status = nullptr;
@@ -847,11 +850,12 @@ DINFER_API int dinfer_attention_decode(const void* q, int64_t ldq, void* out, in
 // The TMA variant (pages of at least 8 tokens): no scratch (the splits fold inside a cluster, at most
 // 16 of them), plus the number of pages of the cache tensor (for the tensor map) and the device status
 // word that a bounded wait sets when it runs out.
-DINFER_API int dinfer_attention_decode_tma(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
-                                           int64_t num_blocks, const int* block_table, int max_blocks,
-                                           const int* cu_seqlens, const int* seq_lens, int B, int H, int Hkv, int D,
-                                           int block_size, float scale, int window, int splits, int* status,
-                                           cudaStream_t stream) {
+// sink != 0: the softmax has one more term of score 0 that carries no value.
+DINFER_API int dinfer_attention_decode_tma_sink(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
+                                                int64_t num_blocks, const int* block_table, int max_blocks,
+                                                const int* cu_seqlens, const int* seq_lens, int B, int H, int Hkv, int D,
+                                                int block_size, float scale, int window, int sink, int splits,
+                                                int* status, cudaStream_t stream) {
   if (B <= 0 || H <= 0 || Hkv <= 0 || H % Hkv || max_blocks <= 0 || num_blocks <= 0)
     return refuse(DINFER_BAD_ARGUMENT, "attention_decode_tma: bad sizes B=%d H=%d Hkv=%d", B, H, Hkv);
   if (!dinfer_attention_decode_supports(D, H / Hkv, block_size) || block_size < 8)
@@ -885,11 +889,20 @@ DINFER_API int dinfer_attention_decode_tma(const void* q, int64_t ldq, void* out
   p.cu_seqlens = cu_seqlens; p.seq_lens = seq_lens; p.H = H; p.Hkv = Hkv; p.group = H / Hkv;
   p.block_size = block_size; p.bs_log2 = 0;
   while ((1 << p.bs_log2) < block_size) ++p.bs_log2;
-  p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.splits = splits;
+  p.window = window; p.sink = sink; p.scale_log2 = scale * 1.4426950408889634f; p.splits = splits;
   p.part_o = nullptr; p.part_ml = nullptr; p.counters = nullptr; p.status = status;
   const int nh8 = (p.group + 7) / 8;
   if (D == 64) return nh8 == 1 ? launch_tma<64, 1>(map, p, B, stream) : launch_tma<64, 2>(map, p, B, stream);
   return nh8 == 1 ? launch_tma<128, 1>(map, p, B, stream) : launch_tma<128, 2>(map, p, B, stream);
+}
+
+DINFER_API int dinfer_attention_decode_tma(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
+                                           int64_t num_blocks, const int* block_table, int max_blocks,
+                                           const int* cu_seqlens, const int* seq_lens, int B, int H, int Hkv, int D,
+                                           int block_size, float scale, int window, int splits, int* status,
+                                           cudaStream_t stream) {
+  return dinfer_attention_decode_tma_sink(q, ldq, out, ldo, cache, num_blocks, block_table, max_blocks, cu_seqlens, seq_lens,
+                                          B, H, Hkv, D, block_size, scale, window, 0, splits, status, stream);
 }
 
 // ---- the entry point that allocates nothing (see attention_decode_static.h)

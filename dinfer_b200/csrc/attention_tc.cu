@@ -38,6 +38,7 @@ struct Params {
   const int* block_table; int max_blocks;
   const int* cu_seqlens; const int* seq_lens;
   int H, Hkv, group, block_size, window;
+  int sink;                    // one more softmax term of score 0 without a value
   float scale_log2;            // scale * log2(e)
   int splits;                  // decode shape only
   float* part_o; float* part_ml;
@@ -292,7 +293,8 @@ __global__ void __launch_bounds__(DECODE ? NT_DECODE : NT_PROMPT, 2) attention_t
     for (int r = 0; r < 2; ++r) {
       const int row = row0 + wrow + g + 8 * r;
       if (row >= rows_total) continue;
-      const float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
+      const float l_all = l_run[r] + (p.sink ? exp2f(-m_run[r]) : 0.f);     // the sink: exp(0 - m), in the denominator only
+      const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
       __nv_bfloat16* dst = p.out + (int64_t)(t0 + row / p.group) * p.ldo + (int64_t)(hk * p.group + row % p.group) * D;
 #pragma unroll
       for (int i = 0; i < D / 8; ++i)
@@ -332,6 +334,7 @@ __global__ void __launch_bounds__(DECODE ? NT_DECODE : NT_PROMPT, 2) attention_t
     }
     const int head = hk * p.group + row;
     if (p.splits == 1) {
+      if (p.sink) L += exp2f(-M);
       p.out[(int64_t)t0 * p.ldo + (int64_t)head * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
     } else {
       const int64_t slot = ((int64_t)b * p.H + head) * p.splits + blockIdx.x;
@@ -358,6 +361,7 @@ __global__ void __launch_bounds__(D) attention_merge_kernel(const Params p) {
     L += p.part_ml[(base + s) * 2 + 1] * f;
     acc += p.part_o[(base + s) * D + d] * f;
   }
+  if (p.sink) L += exp2f(-M);
   p.out[(int64_t)t0 * p.ldo + (int64_t)head * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
 }
 
@@ -415,11 +419,12 @@ DINFER_API int64_t dinfer_attention_tc_scratch_floats(int B, int H, int D, int s
 // block_table [B, max_blocks]; cu_seqlens [B+1]; seq_lens [B] (length after this step).
 // any_decode / any_prefill: whether the batch holds requests with q_len == 1 / q_len > 1.
 // scratch: dinfer_attention_tc_scratch_floats() floats, or null when splits == 1.
-DINFER_API int dinfer_attention_tc(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
-                                   const int* block_table, int max_blocks, const int* cu_seqlens,
-                                   const int* seq_lens, int B, int H, int Hkv, int D, int block_size,
-                                   float scale, int window, int max_q_len, int any_decode, int any_prefill,
-                                   int splits, float* scratch, cudaStream_t stream) {
+// sink != 0: the softmax has one more term of score 0 that carries no value (p_j = exp(s_j) / (1 + sum exp(s_j))).
+DINFER_API int dinfer_attention_tc_sink(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
+                                        const int* block_table, int max_blocks, const int* cu_seqlens,
+                                        const int* seq_lens, int B, int H, int Hkv, int D, int block_size,
+                                        float scale, int window, int sink, int max_q_len, int any_decode,
+                                        int any_prefill, int splits, float* scratch, cudaStream_t stream) {
   if (B <= 0 || H <= 0 || Hkv <= 0 || H % Hkv || block_size <= 0 || max_blocks <= 0)
     return refuse(DINFER_BAD_ARGUMENT, "attention_tc: bad sizes B=%d H=%d Hkv=%d block=%d", B, H, Hkv, block_size);
   if (!dinfer_attention_tc_supports(D, H / Hkv))
@@ -432,10 +437,19 @@ DINFER_API int dinfer_attention_tc(const void* q, int64_t ldq, void* out, int64_
   p.q = (const __nv_bfloat16*)q; p.ldq = ldq; p.out = (__nv_bfloat16*)out; p.ldo = ldo;
   p.cache = (const __nv_bfloat16*)cache; p.block_table = block_table; p.max_blocks = max_blocks;
   p.cu_seqlens = cu_seqlens; p.seq_lens = seq_lens; p.H = H; p.Hkv = Hkv; p.group = H / Hkv;
-  p.block_size = block_size; p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
+  p.block_size = block_size; p.window = window; p.sink = sink; p.scale_log2 = scale * 1.4426950408889634f;
   p.splits = splits; p.part_o = scratch;
   p.part_ml = scratch ? scratch + (int64_t)B * H * splits * D : nullptr;
   if (D == 32) return launch<32>(p, B, max_q_len, any_decode, any_prefill, stream);
   if (D == 64) return launch<64>(p, B, max_q_len, any_decode, any_prefill, stream);
   return launch<128>(p, B, max_q_len, any_decode, any_prefill, stream);
+}
+
+DINFER_API int dinfer_attention_tc(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
+                                   const int* block_table, int max_blocks, const int* cu_seqlens,
+                                   const int* seq_lens, int B, int H, int Hkv, int D, int block_size,
+                                   float scale, int window, int max_q_len, int any_decode, int any_prefill,
+                                   int splits, float* scratch, cudaStream_t stream) {
+  return dinfer_attention_tc_sink(q, ldq, out, ldo, cache, block_table, max_blocks, cu_seqlens, seq_lens, B, H, Hkv, D,
+                                  block_size, scale, window, 0, max_q_len, any_decode, any_prefill, splits, scratch, stream);
 }

@@ -46,6 +46,7 @@ struct Params {
   const int* block_table; int max_blocks;
   const int* cu_seqlens; const int* seq_lens;
   int B, H, Hkv, group, block_size, bs_log2, window;
+  int sink;                    // one more softmax term of score 0 without a value
   int ksplit;                          // CTAs of a cluster that share a row-tile pair's keys (1, 2, 4 or 8)
   float scale_log2;
   int* status;
@@ -424,7 +425,8 @@ attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                                 : nullptr;
     if (ks == 1) {
       if (ok && n_w > 0) {
-        const float inv = l_own > 0.f ? 1.f / l_own : 0.f;
+        const float l_fin = l_own + (p.sink ? exp2f(-m_run) : 0.f);       // the sink: exp(0 - m), in the denominator only
+        const float inv = l_fin > 0.f ? 1.f / l_fin : 0.f;
 #pragma unroll
         for (int c = 0; c < D / 64; ++c) {
           float o[32];
@@ -484,6 +486,7 @@ attention_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
           const float l_p = x_sum[sl * rows_r + rloc];
           if (l_p > 0.f) l_all += l_p * fast_exp2(x_max[sl * rows_r + rloc] - m_all);
         }
+        if (p.sink) l_all += exp2f(-m_all);
         const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
         const float4* recv = reinterpret_cast<const float4*>(smem_dyn + (sK - smem_u32(smem_dyn)));
 #pragma unroll
@@ -608,11 +611,12 @@ DINFER_API int dinfer_attention_umma_supports(int D, int group, int block_size) 
 // key_splits (1, 2, 4 or 8): that many CTAs of a cluster share the keys of a row-tile pair and fold their results
 // through distributed shared memory; for steps with fewer row tiles than the device has SMs.
 // q: [T, ...] rows of stride ldq with head h at h*D (all H heads); cache [num_blocks, 2, Hkv, block, D] bf16.
-DINFER_API int dinfer_attention_umma(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
-                                     int64_t num_blocks, const int* block_table, int max_blocks,
-                                     const int* cu_seqlens, const int* seq_lens, int T, int B, int H, int Hkv, int D,
-                                     int block_size, float scale, int window, int max_q_len, int pair_bound,
-                                     int key_splits, int* status, cudaStream_t stream) {
+// sink != 0: the softmax has one more term of score 0 that carries no value.
+DINFER_API int dinfer_attention_umma_sink(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
+                                          int64_t num_blocks, const int* block_table, int max_blocks,
+                                          const int* cu_seqlens, const int* seq_lens, int T, int B, int H, int Hkv, int D,
+                                          int block_size, float scale, int window, int sink, int max_q_len,
+                                          int pair_bound, int key_splits, int* status, cudaStream_t stream) {
   if (T <= 0 || B <= 0 || H <= 0 || Hkv <= 0 || H % Hkv || max_blocks <= 0 || num_blocks <= 0)
     return refuse(DINFER_BAD_ARGUMENT, "attention_umma: bad sizes T=%d B=%d H=%d Hkv=%d", T, B, H, Hkv);
   const int group = H / Hkv;
@@ -658,11 +662,20 @@ DINFER_API int dinfer_attention_umma(const void* q, int64_t ldq, void* out, int6
   p.cu_seqlens = cu_seqlens; p.seq_lens = seq_lens; p.H = H; p.Hkv = Hkv; p.group = group; p.block_size = block_size;
   p.bs_log2 = 0;
   while ((1 << p.bs_log2) < block_size) ++p.bs_log2;
-  p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+  p.window = window; p.sink = sink; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
   p.ksplit = key_splits; p.B = B;
   // pairs of 128-row tiles in the batch: the caller's bound, or every request taken for the longest
   int64_t pairs = pair_bound > 0 ? pair_bound : (int64_t)B * (((int64_t)max_q_len * group + 2 * BM - 1) / (2 * BM));
   if (pairs > 65535) return refuse(DINFER_BAD_ARGUMENT, "attention_umma: %lld row-tile pairs are too many for the grid", (long long)pairs);
   dim3 grid(Hkv * key_splits, (unsigned)pairs, 1);
   return D == 64 ? launch<64>(mq, mkv, p, grid, stream) : launch<128>(mq, mkv, p, grid, stream);
+}
+
+DINFER_API int dinfer_attention_umma(const void* q, int64_t ldq, void* out, int64_t ldo, const void* cache,
+                                     int64_t num_blocks, const int* block_table, int max_blocks,
+                                     const int* cu_seqlens, const int* seq_lens, int T, int B, int H, int Hkv, int D,
+                                     int block_size, float scale, int window, int max_q_len, int pair_bound,
+                                     int key_splits, int* status, cudaStream_t stream) {
+  return dinfer_attention_umma_sink(q, ldq, out, ldo, cache, num_blocks, block_table, max_blocks, cu_seqlens, seq_lens, T, B,
+                                    H, Hkv, D, block_size, scale, window, 0, max_q_len, pair_bound, key_splits, status, stream);
 }

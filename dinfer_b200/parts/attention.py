@@ -102,8 +102,8 @@ class GQAttention(Mixer):
         return KvCacheNeed(self.Hkv, max(self.D, self.Dv), self.window, int(self.page_size) if self.page_size else None)
 
     def _fast(self, dtype) -> bool:
-        """Whether the tensor-core kernels take this attention: keys and values of one width, no sink."""
-        return self.Dv == self.D and not self.sink and attention_ops.tc_supported(dtype, self.D, self.H // self.Hkv)
+        """Whether the tensor-core kernels take this attention: keys and values of one width."""
+        return self.Dv == self.D and attention_ops.tc_supported(dtype, self.D, self.H // self.Hkv)
 
     def kernel_libraries(self):
         att = ["attention_generic"]
@@ -158,10 +158,11 @@ class GQAttention(Mixer):
         if self._fast(q.dtype):
             splits = ctx.decode_splits or attention_ops.decode_splits(ctx.num_reqs, self.Hkv, ctx.max_seq_len)
             tc_decode = ctx.any_decode
-            if ctx.any_decode and attention_ops.decode_supported(q.dtype, self.D, self.H // self.Hkv, g.block_size):
+            if ctx.any_decode and attention_ops.decode_supported(q.dtype, self.D, self.H // self.Hkv, g.block_size) \
+                    and (g.block_size >= 8 or not self.sink):
                 # decoded tokens: the kernel made for them (keys on the tile's rows, in-kernel fold)
                 attention_ops.attention_decode(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, self.H,
-                                               self.Hkv, self.D, self.scale, window, splits)
+                                               self.Hkv, self.D, self.scale, window, splits, sink=self.sink)
                 tc_decode = False
             tc_prefill = ctx.any_prefill
             if ctx.any_prefill and attention_ops.umma_supported(q.dtype, self.D, self.H // self.Hkv, g.block_size):
@@ -178,15 +179,17 @@ class GQAttention(Mixer):
                 if ((ctx.max_prefill_seq_len or ctx.max_seq_len) <= attention_ops.UMMA_SHORT_CONTEXT
                         and attention_ops.umma64_supported(q.dtype, self.D, self.H // self.Hkv, g.block_size)):
                     attention_ops.attention_umma64(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, self.H,
-                                                   self.Hkv, self.D, self.scale, window, ctx.max_q_len, shape[1])
+                                                   self.Hkv, self.D, self.scale, window, ctx.max_q_len, shape[1],
+                                                   sink=self.sink)
                 else:
                     attention_ops.attention_umma(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, self.H,
-                                                 self.Hkv, self.D, self.scale, window, ctx.max_q_len, shape[0], shape[1])
+                                                 self.Hkv, self.D, self.scale, window, ctx.max_q_len, shape[0], shape[1],
+                                                 sink=self.sink)
                 tc_prefill = False
             if tc_decode or tc_prefill:
                 attention_ops.attention_tc(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.seq_lens, self.H,
                                            self.Hkv, self.D, self.scale, window, ctx.max_q_len, tc_decode,
-                                           tc_prefill, splits)
+                                           tc_prefill, splits, sink=self.sink)
         else:
             ops.attention_generic(q, out, kv, g.block_table, ctx.cu_seqlens, ctx.positions, self.H, self.Hkv,
                                   self.D, self.scale, window, v_dim=self.Dv, sink=self.sink)

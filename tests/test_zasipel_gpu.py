@@ -136,6 +136,64 @@ def test_attention_key_at_the_windows_edge(new, back):
     assert (moved > 1e-2) == (back <= 0), moved
 
 
+@pytest.mark.parametrize("D, H_, G, block_size", [(64, 4, 2, 16), (128, 8, 2, 16), (64, 2, 2, 64), (128, 4, 1, 8), (32, 4, 4, 4)])
+def test_tensor_core_attention_with_sink(D, H_, G, block_size):
+    """The tensor-core kernels (tcgen05 prompt kernels with 64- and 128-key tiles, the TMA decode kernel with its key
+    splits, the mma.sync kernel) with a window and the sink, against the plain-arithmetic kernel on the same cache:
+    a prompt from position 0, a portion behind a history longer than the window, decoded tokens."""
+    from dinfer_b200.kernels import attention_ops, ops
+    g = torch.Generator().manual_seed(D + H_)
+    window, scale = 150, 0.6 * D ** -0.5
+    seqs = [(0, 300), (700, 1), (420, 140), (0, 1), (149, 1), (151, 1)]
+    total = [a + b for a, b in seqs]
+    pages = [(n + block_size - 1) // block_size for n in total]
+    perm = torch.randperm(sum(pages), generator=g)
+    tab = torch.full((len(seqs), max(pages)), -1, dtype=torch.int32)
+    at = 0
+    for b, n in enumerate(pages):
+        tab[b, :n] = perm[at:at + n]
+        at += n
+    cache = torch.randn(sum(pages), 2, G, block_size, D, generator=g).to(torch.bfloat16).cuda()
+    T = sum(b for _, b in seqs)
+    q = torch.randn(T, H_ * D, generator=g).to(torch.bfloat16).cuda()
+    pos = torch.cat([torch.arange(a, a + b) for a, b in seqs]).to(torch.int32).cuda()
+    cu = i32(np.concatenate([[0], np.cumsum([b for _, b in seqs])]))
+    seq_lens, table = i32(total), dev(tab)
+    want = torch.empty(T, H_ * D, dtype=torch.bfloat16, device="cuda")
+    ops.attention_generic(q, want, cache, table, cu, pos, H_, G, D, scale, window, sink=True)
+    plain = torch.empty_like(want)
+    ops.attention_generic(q, plain, cache, table, cu, pos, H_, G, D, scale, window, sink=False)
+    assert float((want.float() - plain.float()).abs().max()) > 0.05          # the sink matters at these scores
+    prompt_rows = torch.cat([torch.arange(int(cu[i]), int(cu[i + 1])) for i, (_, b) in enumerate(seqs) if b > 1]).cuda()
+    decode_rows = torch.cat([torch.arange(int(cu[i]), int(cu[i + 1])) for i, (_, b) in enumerate(seqs) if b == 1]).cuda()
+    group = H_ // G
+
+    def close(got, rows, what):
+        d = float((got[rows].float() - want[rows].float()).abs().max())
+        assert d <= 2e-2, (what, d)
+
+    for splits in (1, 4):
+        got = torch.full_like(want, float("nan"))
+        attention_ops.attention_tc(q, got, cache, table, cu, seq_lens, H_, G, D, scale, window, 300, True, True, splits, sink=True)
+        close(got, torch.arange(T).cuda(), f"mma.sync kernel, {splits} splits")
+    if attention_ops.decode_supported(torch.bfloat16, D, group, block_size) and block_size >= 8:
+        for splits in (1, 2, 8):
+            got = torch.full_like(want, float("nan"))
+            attention_ops.attention_decode(q, got, cache, table, cu, seq_lens, H_, G, D, scale, window, splits, sink=True)
+            close(got, decode_rows, f"decode kernel, {splits} splits")
+    if attention_ops.umma_supported(torch.bfloat16, D, group, block_size):
+        lens = [b for _, b in seqs]
+        bound = attention_ops.umma_pair_bound(lens, group)
+        for ks in (1, 2):
+            got = torch.full_like(want, float("nan"))
+            attention_ops.attention_umma(q, got, cache, table, cu, seq_lens, H_, G, D, scale, window, 300, ks, bound, sink=True)
+            close(got, prompt_rows, f"tcgen05 kernel, keys shared {ks} ways")
+        if attention_ops.umma64_supported(torch.bfloat16, D, group, block_size):
+            got = torch.full_like(want, float("nan"))
+            attention_ops.attention_umma64(q, got, cache, table, cu, seq_lens, H_, G, D, scale, window, 300, bound, sink=True)
+            close(got, prompt_rows, "tcgen05 kernel with 64-key tiles")
+
+
 # ---------------------------------------------------------------- the delta rule
 def delta_inputs(T, H_, G, dk, dv, per_channel, seed):
     g = torch.Generator().manual_seed(seed)
