@@ -34,17 +34,21 @@ __device__ __forceinline__ int request_of(const int* __restrict__ cu, int B, int
 }
 
 // ---------------------------------------------------------------- prep
+constexpr int PREP_CHUNK = 512;
 // P [T, ldp]: columns q (G*dk) at cq, k (G*dk) at ck, v (H*dv) at cv, b (H) at cb.  A [T, lda]: the decay's input,
 // H or H*dk wide.  conv_w [C, taps] with C = 2*G*dk + H*dv (q, k, v order).  hist [slots, hist_stride] (taps-1 rows of C).
 template <typename TA>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 delta_prep_kernel(const TA* __restrict__ P, int64_t ldp, int cq, int ck, int cv, int cb, const TA* __restrict__ A,
                   int64_t lda, const float* __restrict__ conv_w, const float* __restrict__ A_log,
                   const float* __restrict__ dt_bias, const float* __restrict__ hist, int64_t hist_stride,
                   const int* __restrict__ cu, const int* __restrict__ slots, const int* __restrict__ fresh, int B,
                   float* __restrict__ qn, float* __restrict__ kn, float* __restrict__ vv, float* __restrict__ beta,
                   float* __restrict__ decay, int H, int G, int dk, int dv, int taps, int per_channel) {
-  extern __shared__ float y[];                             // the token's q | k channels after convolution and silu
+  // the jobs of a token, one block each (blockIdx.y): a q head, a k head, PREP_CHUNK value channels, or PREP_CHUNK
+  // decays (the first of those also the token's betas)
+  extern __shared__ float y[];                             // a head's channels after convolution and silu
+  __shared__ float red[33];
   pdl_enter();
   const int t = blockIdx.x;
   const int b = request_of(cu, B, t);
@@ -52,7 +56,8 @@ delta_prep_kernel(const TA* __restrict__ P, int64_t ldp, int cq, int ck, int cv,
   const bool have_hist = !fresh[b];
   const float* hb = hist + (int64_t)slots[b] * hist_stride;
   const int nq = G * dk, nv = H * dv, C = 2 * nq + nv;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+  const int nvb = (nv + PREP_CHUNK - 1) / PREP_CHUNK;
+  auto conv = [&](int c) {                                 // channel c of q | k | v: the convolution, then silu
     const int col = c < nq ? cq + c : (c < 2 * nq ? ck + c - nq : cv + c - 2 * nq);
     float acc = 0.f;
     for (int d = 0; d < taps; ++d) {                       // d tokens back
@@ -61,25 +66,35 @@ delta_prep_kernel(const TA* __restrict__ P, int64_t ldp, int cq, int ck, int cv,
       else if (have_hist) x = hb[(int64_t)(taps - 1 + i - d) * C + c];
       acc = fmaf(conv_w[(int64_t)c * taps + taps - 1 - d], x, acc);
     }
-    const float s = silu_f(acc);
-    if (c < 2 * nq) y[c] = s; else vv[(int64_t)t * nv + c - 2 * nq] = s;
-  }
-  __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
-  for (int hd = warp; hd < 2 * G; hd += nwarp) {           // q heads, then k heads
-    const float* x = y + hd * dk;
+    return silu_f(acc);
+  };
+  int job = blockIdx.y;
+  if (job < 2 * G) {                                       // q heads, then k heads: unit vectors
     float ss = 0.f;
-    for (int e = lane; e < dk; e += 32) ss += x[e] * x[e];
-    ss = warp_sum(ss);
+    for (int e = threadIdx.x; e < dk; e += blockDim.x) {
+      const float v = conv(job * dk + e);
+      y[e] = v;
+      ss += v * v;
+    }
+    ss = block_sum(ss, red);
     float r = 1.f / sqrtf(ss + 1e-6f);
-    if (hd < G) r *= 1.f / sqrtf((float)dk);
-    float* o = hd < G ? qn + (int64_t)t * nq + hd * dk : kn + (int64_t)t * nq + (hd - G) * dk;
-    for (int e = lane; e < dk; e += 32) o[e] = x[e] * r;
+    if (job < G) r *= 1.f / sqrtf((float)dk);
+    float* o = job < G ? qn + (int64_t)t * nq + job * dk : kn + (int64_t)t * nq + (job - G) * dk;
+    for (int e = threadIdx.x; e < dk; e += blockDim.x) o[e] = y[e] * r;
+    return;
   }
-  for (int h = threadIdx.x; h < H; h += blockDim.x)
-    beta[(int64_t)t * H + h] = sigmoid_f(to_f32<TA>(P[(int64_t)t * ldp + cb + h]));
+  job -= 2 * G;
+  if (job < nvb) {
+    for (int c = job * PREP_CHUNK + threadIdx.x; c < min(nv, (job + 1) * PREP_CHUNK); c += blockDim.x)
+      vv[(int64_t)t * nv + c] = conv(2 * nq + c);
+    return;
+  }
+  job -= nvb;
+  if (job == 0)
+    for (int h = threadIdx.x; h < H; h += blockDim.x)
+      beta[(int64_t)t * H + h] = sigmoid_f(to_f32<TA>(P[(int64_t)t * ldp + cb + h]));
   const int nd = per_channel ? H * dk : H;
-  for (int c = threadIdx.x; c < nd; c += blockDim.x) {
+  for (int c = job * PREP_CHUNK + threadIdx.x; c < min(nd, (job + 1) * PREP_CHUNK); c += blockDim.x) {
     const int h = per_channel ? c / dk : c;
     const float a = to_f32<TA>(A[(int64_t)t * lda + c]) + dt_bias[c];
     decay[(int64_t)t * nd + c] = expf(-expf(A_log[h]) * softplus_f(a));
@@ -197,6 +212,141 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
   }
 }
 
+
+__device__ __forceinline__ void cp_async_f4(float* smem, const float* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_f1(float* smem, const float* gmem) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit_group() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// The same recurrence with a lane's share of its column in registers, for key widths that split evenly: LPC lanes share
+// a column, each owns R = dk / LPC rows, four at a time ((m * LPC + s) * 4 .. + 3, so that the lanes of a column read
+// neighbouring 16-byte pieces of k, q and the decay from shared memory).  A tile of TT tokens' q, k, decay, and the
+// block's columns of v with beta, is staged in shared memory while the tile before it is worked on (two buffers), so
+// that the walk over the tokens never waits for global memory.
+constexpr int F_TT = 16;
+
+template <int R, int LPC>
+__global__ void __launch_bounds__(R_WARPS * 32)
+delta_recurrence_reg_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vv,
+                            const float* __restrict__ beta, const float* __restrict__ decay, float* __restrict__ state,
+                            int64_t state_stride, const int* __restrict__ cu, const int* __restrict__ slots,
+                            const int* __restrict__ fresh, float* __restrict__ out, int H, int G, int dv,
+                            int per_channel) {
+  constexpr int DK = R * LPC, COLS = 32 / LPC, BC = COLS * R_WARPS;
+  constexpr int TILE = F_TT * (3 * DK + BC + 1);          // floats of one staged tile: q, k, decay | v | beta
+  extern __shared__ __align__(16) float smf[];
+  pdl_enter();
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int start = cu[b], n = cu[b + 1] - start;
+  if (n <= 0) return;
+  const int c0 = blockIdx.x * BC;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int lc = warp * COLS + lane / LPC, sub = lane % LPC;
+  const int col = c0 + lc;
+  const bool live = col < dv;
+  const int g = h / (H / G);
+  float* Sg = state + (int64_t)slots[b] * state_stride + (int64_t)h * DK * dv;
+  float S[R];
+  if (!fresh[b] && live) {
+#pragma unroll
+    for (int m = 0; m < R / 4; ++m)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) S[m * 4 + j] = Sg[(int64_t)((m * LPC + sub) * 4 + j) * dv + col];
+  } else {
+#pragma unroll
+    for (int r = 0; r < R; ++r) S[r] = 0.f;
+  }
+  const int nq = G * DK, nd = per_channel ? H * DK : H;
+  const int64_t ldv = (int64_t)H * dv;
+  auto stage = [&](int t0, float* buf) {                   // cp.async: 16-byte pieces of q, k, decay; 4-byte ones of the rest
+    const int tt = min(F_TT, n - t0);
+    float* sq = buf;
+    float* sk = sq + F_TT * DK;
+    float* sg = sk + F_TT * DK;
+    float* sv = sg + F_TT * DK;
+    float* sb = sv + F_TT * BC;
+    for (int idx = threadIdx.x; idx < tt * (DK / 4); idx += blockDim.x) {
+      const int j = idx / (DK / 4), e = (idx % (DK / 4)) * 4;
+      const int64_t t = start + t0 + j;
+      cp_async_f4(sq + j * DK + e, qn + t * nq + g * DK + e);
+      cp_async_f4(sk + j * DK + e, kn + t * nq + g * DK + e);
+      if (per_channel) cp_async_f4(sg + j * DK + e, decay + t * nd + h * DK + e);
+    }
+    for (int idx = threadIdx.x; idx < tt * BC; idx += blockDim.x) {
+      const int j = idx / BC, c = idx % BC;
+      if (c0 + c < dv) cp_async_f1(sv + idx, vv + (int64_t)(start + t0 + j) * ldv + (int64_t)h * dv + c0 + c);
+    }
+    for (int j = threadIdx.x; j < tt; j += blockDim.x) {
+      cp_async_f1(sb + j, beta + (int64_t)(start + t0 + j) * H + h);
+      if (!per_channel) cp_async_f1(sg + j, decay + (int64_t)(start + t0 + j) * nd + h);
+    }
+    cp_async_commit_group();
+  };
+  stage(0, smf);
+  int which = 0;
+  for (int t0 = 0; t0 < n; t0 += F_TT, which ^= 1) {
+    const int tt = min(F_TT, n - t0);
+    if (t0 + F_TT < n) { stage(t0 + F_TT, smf + (which ^ 1) * TILE); cp_async_wait_group<1>(); }
+    else cp_async_wait_group<0>();
+    __syncthreads();
+    const float* sq = smf + which * TILE;
+    const float* sk = sq + F_TT * DK;
+    const float* sg = sk + F_TT * DK;
+    const float* sv = sg + F_TT * DK;
+    const float* sb = sv + F_TT * BC;
+    for (int j = 0; j < tt; ++j) {
+      const float4* k4 = reinterpret_cast<const float4*>(sk + j * DK);
+      const float4* q4 = reinterpret_cast<const float4*>(sq + j * DK);
+      const float4* g4 = reinterpret_cast<const float4*>(sg + j * DK);
+      const float gs = per_channel ? 1.f : sg[j];
+      float kr[R];
+      float read = 0.f;
+#pragma unroll
+      for (int m = 0; m < R / 4; ++m) {
+        const float4 kk = k4[m * LPC + sub];
+        float4 gg = make_float4(gs, gs, gs, gs);
+        if (per_channel) gg = g4[m * LPC + sub];
+        kr[m * 4] = kk.x; kr[m * 4 + 1] = kk.y; kr[m * 4 + 2] = kk.z; kr[m * 4 + 3] = kk.w;
+        S[m * 4] *= gg.x; S[m * 4 + 1] *= gg.y; S[m * 4 + 2] *= gg.z; S[m * 4 + 3] *= gg.w;
+        read = fmaf(S[m * 4], kk.x, read);
+        read = fmaf(S[m * 4 + 1], kk.y, read);
+        read = fmaf(S[m * 4 + 2], kk.z, read);
+        read = fmaf(S[m * 4 + 3], kk.w, read);
+      }
+#pragma unroll
+      for (int o = 1; o < LPC; o <<= 1) read += __shfl_xor_sync(0xffffffffu, read, o);
+      const float u = sb[j] * (sv[j * BC + lc] - read);
+      float acc = 0.f;
+#pragma unroll
+      for (int m = 0; m < R / 4; ++m) {
+        const float4 qq = q4[m * LPC + sub];
+        S[m * 4] = fmaf(kr[m * 4], u, S[m * 4]);
+        S[m * 4 + 1] = fmaf(kr[m * 4 + 1], u, S[m * 4 + 1]);
+        S[m * 4 + 2] = fmaf(kr[m * 4 + 2], u, S[m * 4 + 2]);
+        S[m * 4 + 3] = fmaf(kr[m * 4 + 3], u, S[m * 4 + 3]);
+        acc = fmaf(S[m * 4], qq.x, acc);
+        acc = fmaf(S[m * 4 + 1], qq.y, acc);
+        acc = fmaf(S[m * 4 + 2], qq.z, acc);
+        acc = fmaf(S[m * 4 + 3], qq.w, acc);
+      }
+#pragma unroll
+      for (int o = 1; o < LPC; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (live && sub == 0) out[(int64_t)(start + t0 + j) * ldv + (int64_t)h * dv + col] = acc;
+    }
+    __syncthreads();                                       // the buffer is staged again two tiles on
+  }
+  if (live) {
+#pragma unroll
+    for (int m = 0; m < R / 4; ++m)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) Sg[(int64_t)((m * LPC + sub) * 4 + j) * dv + col] = S[m * 4 + j];
+  }
+}
+
 // ---------------------------------------------------------------- output norm and gate
 // one warp per (token, head): y = o * rsqrt(mean(o^2) + eps) * w * act(gate)
 template <typename TA>
@@ -232,13 +382,15 @@ DINFER_API int dinfer_delta_prep(const void* P, int64_t ldp, int cq, int ck, int
                                  int dv, int taps, int per_channel, int act_dtype, cudaStream_t stream) {
   if (T < 0 || B <= 0 || H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || taps <= 0)
     return refuse(DINFER_BAD_ARGUMENT, "delta_prep: bad sizes T=%d B=%d H=%d G=%d dk=%d dv=%d taps=%d", T, B, H, G, dk, dv, taps);
-  const size_t smem = (size_t)2 * G * dk * sizeof(float);
-  if (smem > 200 * 1024) return refuse(DINFER_BAD_ARGUMENT, "delta_prep: %d key channels above the limit", 2 * G * dk);
+  const size_t smem = (size_t)dk * sizeof(float);
+  if (smem > 48 * 1024) return refuse(DINFER_BAD_ARGUMENT, "delta_prep: %d key channels above the limit", dk);
   if (T == 0) return 0;
   const int nq = G * dk, nv = H * dv;
+  const int nd = per_channel ? H * dk : H;
+  const int jobs = 2 * G + (nv + PREP_CHUNK - 1) / PREP_CHUNK + (nd + PREP_CHUNK - 1) / PREP_CHUNK;
+  if (jobs > 65535) return refuse(DINFER_BAD_ARGUMENT, "delta_prep: too many heads for the grid");
   DINFER_DISPATCH_DTYPE(act_dtype, TA, {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(delta_prep_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    launch_pdl(delta_prep_kernel<TA>, dim3(T), dim3(256), smem, stream, (const TA*)P, ldp, cq, ck, cv, cb, (const TA*)A,
+    launch_pdl(delta_prep_kernel<TA>, dim3(T, jobs), dim3(128), smem, stream, (const TA*)P, ldp, cq, ck, cv, cb, (const TA*)A,
                lda, conv_w, A_log, dt_bias, (const float*)hist, hist_stride, cu, slots, fresh, B, qn, kn, vv, beta,
                decay, H, G, dk, dv, taps, per_channel);
     if (cudaError_t e = cudaGetLastError(); e != cudaSuccess) return refuse((int)e, "delta_prep: %s", cudaGetErrorString(e));
@@ -260,6 +412,30 @@ DINFER_API int dinfer_delta_recurrence(const float* qn, const float* kn, const f
                                        int dv, int per_channel, cudaStream_t stream) {
   if (B <= 0 || H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || H > 65535 || B > 65535)
     return refuse(DINFER_BAD_ARGUMENT, "delta_recurrence: bad sizes B=%d H=%d G=%d dk=%d dv=%d", B, H, G, dk, dv);
+  // key widths that split evenly over the lanes of a column (and rows that cp.async can fetch in 16-byte pieces): the
+  // kernel that keeps the state in registers
+  if ((dk == 16 || dk == 32 || dk == 64 || dk == 128 || dk == 256) && (G * dk) % 4 == 0 &&
+      !(reinterpret_cast<uintptr_t>(qn) & 15) && !(reinterpret_cast<uintptr_t>(kn) & 15) && !(reinterpret_cast<uintptr_t>(decay) & 15)) {
+#define GO_REG(R_, LPC_)                                                                                            \
+  do {                                                                                                              \
+    constexpr int BC_ = 32 / LPC_ * R_WARPS;                                                                        \
+    const size_t sm = (size_t)2 * F_TT * (3 * R_ * LPC_ + BC_ + 1) * sizeof(float);                                 \
+    static bool opted = false;                                                                                      \
+    if (sm > 48 * 1024 && !opted) {                                                                                 \
+      cudaFuncSetAttribute(delta_recurrence_reg_kernel<R_, LPC_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); \
+      opted = true;                                                                                                 \
+    }                                                                                                               \
+    launch_pdl(delta_recurrence_reg_kernel<R_, LPC_>, dim3((dv + BC_ - 1) / BC_, H, B), dim3(R_WARPS * 32), sm, stream, qn, \
+               kn, vv, beta, decay, state, state_stride, cu, slots, fresh, out, H, G, dv, per_channel);             \
+    return cuda_status("delta_recurrence");                                                                         \
+  } while (0)
+    if (dk == 16) GO_REG(16, 1);
+    if (dk == 32) GO_REG(16, 2);
+    if (dk == 64) GO_REG(16, 4);
+    if (dk == 128) GO_REG(16, 8);
+    GO_REG(32, 8);
+#undef GO_REG
+  }
   // lanes that share a column: enough that a lane owns about 16 rows, fewer for a narrow state
   const int lpc = dk >= 128 ? 8 : (dk >= 48 ? 4 : (dk >= 24 ? 2 : 1));
   const int bc = 32 / lpc * R_WARPS;

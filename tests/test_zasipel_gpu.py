@@ -206,7 +206,8 @@ def delta_inputs(T, H_, G, dk, dv, per_channel, seed):
 
 
 @pytest.mark.parametrize("per_channel", [False, True])
-@pytest.mark.parametrize("H_, G, dk, dv", [(4, 2, 16, 24), (3, 3, 128, 40), (2, 2, 24, 128), (1, 1, 12, 20), (2, 1, 64, 16), (5, 5, 200, 7)])
+@pytest.mark.parametrize("H_, G, dk, dv", [(4, 2, 16, 24), (3, 3, 128, 40), (2, 2, 24, 128), (1, 1, 12, 20), (2, 1, 64, 16), (5, 5, 200, 7),
+                                          (2, 1, 32, 33), (1, 1, 256, 20)])
 def test_delta_recurrence(H_, G, dk, dv, per_channel):
     """Three requests in one batch against each alone in the plain implementation; then the same tokens in portions
     (of 1, 2 and more tokens) through slots that another request has used before: the carried state is exact, so
