@@ -298,13 +298,17 @@ delta_recurrence_reg_kernel(const float* __restrict__ qn, const float* __restric
     const float* sg = sk + F_TT * DK;
     const float* sv = sg + F_TT * DK;
     const float* sb = sv + F_TT * BC;
+    // The read S^T k of a token needs the state the token before left, so that chain is the kernel's pace: decay,
+    // four partial sums, the lanes' exchange, u, the update.  The read-out S^T q is off that chain: its partial sum
+    // waits one token and is exchanged between the lanes together with the next token's read.
+    float acc_prev = 0.f;
     for (int j = 0; j < tt; ++j) {
       const float4* k4 = reinterpret_cast<const float4*>(sk + j * DK);
       const float4* q4 = reinterpret_cast<const float4*>(sq + j * DK);
       const float4* g4 = reinterpret_cast<const float4*>(sg + j * DK);
       const float gs = per_channel ? 1.f : sg[j];
       float kr[R];
-      float read = 0.f;
+      float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
 #pragma unroll
       for (int m = 0; m < R / 4; ++m) {
         const float4 kk = k4[m * LPC + sub];
@@ -312,15 +316,20 @@ delta_recurrence_reg_kernel(const float* __restrict__ qn, const float* __restric
         if (per_channel) gg = g4[m * LPC + sub];
         kr[m * 4] = kk.x; kr[m * 4 + 1] = kk.y; kr[m * 4 + 2] = kk.z; kr[m * 4 + 3] = kk.w;
         S[m * 4] *= gg.x; S[m * 4 + 1] *= gg.y; S[m * 4 + 2] *= gg.z; S[m * 4 + 3] *= gg.w;
-        read = fmaf(S[m * 4], kk.x, read);
-        read = fmaf(S[m * 4 + 1], kk.y, read);
-        read = fmaf(S[m * 4 + 2], kk.z, read);
-        read = fmaf(S[m * 4 + 3], kk.w, read);
+        r0 = fmaf(S[m * 4], kk.x, r0);
+        r1 = fmaf(S[m * 4 + 1], kk.y, r1);
+        r2 = fmaf(S[m * 4 + 2], kk.z, r2);
+        r3 = fmaf(S[m * 4 + 3], kk.w, r3);
       }
+      float read = (r0 + r1) + (r2 + r3);
 #pragma unroll
-      for (int o = 1; o < LPC; o <<= 1) read += __shfl_xor_sync(0xffffffffu, read, o);
+      for (int o = 1; o < LPC; o <<= 1) {
+        read += __shfl_xor_sync(0xffffffffu, read, o);
+        acc_prev += __shfl_xor_sync(0xffffffffu, acc_prev, o);
+      }
+      if (j > 0 && live && sub == 0) out[(int64_t)(start + t0 + j - 1) * ldv + (int64_t)h * dv + col] = acc_prev;
       const float u = sb[j] * (sv[j * BC + lc] - read);
-      float acc = 0.f;
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
       for (int m = 0; m < R / 4; ++m) {
         const float4 qq = q4[m * LPC + sub];
@@ -328,15 +337,16 @@ delta_recurrence_reg_kernel(const float* __restrict__ qn, const float* __restric
         S[m * 4 + 1] = fmaf(kr[m * 4 + 1], u, S[m * 4 + 1]);
         S[m * 4 + 2] = fmaf(kr[m * 4 + 2], u, S[m * 4 + 2]);
         S[m * 4 + 3] = fmaf(kr[m * 4 + 3], u, S[m * 4 + 3]);
-        acc = fmaf(S[m * 4], qq.x, acc);
-        acc = fmaf(S[m * 4 + 1], qq.y, acc);
-        acc = fmaf(S[m * 4 + 2], qq.z, acc);
-        acc = fmaf(S[m * 4 + 3], qq.w, acc);
+        a0 = fmaf(S[m * 4], qq.x, a0);
+        a1 = fmaf(S[m * 4 + 1], qq.y, a1);
+        a2 = fmaf(S[m * 4 + 2], qq.z, a2);
+        a3 = fmaf(S[m * 4 + 3], qq.w, a3);
       }
-#pragma unroll
-      for (int o = 1; o < LPC; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (live && sub == 0) out[(int64_t)(start + t0 + j) * ldv + (int64_t)h * dv + col] = acc;
+      acc_prev = (a0 + a1) + (a2 + a3);
     }
+#pragma unroll
+    for (int o = 1; o < LPC; o <<= 1) acc_prev += __shfl_xor_sync(0xffffffffu, acc_prev, o);
+    if (live && sub == 0) out[(int64_t)(start + t0 + tt - 1) * ldv + (int64_t)h * dv + col] = acc_prev;
     __syncthreads();                                       // the buffer is staged again two tiles on
   }
   if (live) {

@@ -360,52 +360,67 @@ DINFER_API int dinfer_scaled_add(float* residual, const void* d1, const void* s1
 // All of it in 32-bit, the row kept in shared memory.  One block per row.
 namespace {
 
-template <typename TA, typename TW>
+template <typename TA, typename TW, int VEC>
 __global__ void __launch_bounds__(1024)
 branch_norm_kernel(const TA* __restrict__ a, const TW* __restrict__ wa, const TA* __restrict__ b,
                    const TW* __restrict__ wb, float coef, float inner_eps, const TW* __restrict__ w, float eps,
                    float* __restrict__ residual, float* __restrict__ out32, TA* __restrict__ cast, int h) {
-  extern __shared__ float row[];
+  extern __shared__ __align__(16) float rows_sm[];        // the row of a, and of b behind it: each is read from memory once
   __shared__ float red[33];
+  float* ya = rows_sm;
+  float* yb = rows_sm + h;
   pdl_enter();
   const int64_t r = blockIdx.x;
   const TA* pa = a + r * h;
   const TA* pb = b ? b + r * h : nullptr;
   float sa = 0.f, sb = 0.f;
-  if (wa) {
-    for (int i = threadIdx.x; i < h; i += blockDim.x) {
-      const float x = to_f32<TA>(pa[i]);
-      sa += x * x;
-      if (pb) { const float y = to_f32<TA>(pb[i]); sb += y * y; }
+  for (int i = threadIdx.x * VEC; i < h; i += blockDim.x * VEC) {
+    float x[4], y[4];
+    if (VEC == 4) { load4<TA>(pa + i, x); if (pb) load4<TA>(pb + i, y); }
+    else { x[0] = to_f32<TA>(pa[i]); if (pb) y[0] = to_f32<TA>(pb[i]); }
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      ya[i + j] = x[j];
+      sa += x[j] * x[j];
+      if (pb) { yb[i + j] = y[j]; sb += y[j] * y[j]; }
     }
+  }
+  float ss = sa;                                           // one branch without an inner norm: y = a
+  if (wa) {
     sa = block_sum(sa, red);
     if (pb) sb = block_sum(sb, red);
-  }
-  const float ra = wa ? 1.f / sqrtf(sa / (float)h + inner_eps) : 1.f;
-  const float rb = pb ? 1.f / sqrtf(sb / (float)h + inner_eps) : 0.f;
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < h; i += blockDim.x) {
-    float y = to_f32<TA>(pa[i]);
-    if (wa) {
-      y = y * ra * to_f32<TW>(wa[i]);
-      if (pb) y += to_f32<TA>(pb[i]) * rb * to_f32<TW>(wb[i]);
+    const float ra = 1.f / sqrtf(sa / (float)h + inner_eps);
+    const float rb = pb ? 1.f / sqrtf(sb / (float)h + inner_eps) : 0.f;
+    ss = 0.f;
+    for (int i = threadIdx.x; i < h; i += blockDim.x) {    // behind the barriers of the sums above
+      float y = ya[i] * ra * to_f32<TW>(wa[i]);
+      if (pb) y += yb[i] * rb * to_f32<TW>(wb[i]);
       y *= coef;
+      ya[i] = y;
+      ss += y * y;
     }
-    row[i] = y;
-    ss += y * y;
   }
   float rn = 1.f;
   if (w) rn = 1.f / sqrtf(block_sum(ss, red) / (float)h + eps);
-  for (int i = threadIdx.x; i < h; i += blockDim.x) {
-    float z = row[i];
-    if (w) z = z * rn * to_f32<TW>(w[i]);
-    if (residual) {
-      z += residual[r * h + i];
-      residual[r * h + i] = z;
+  if (wa && VEC == 4) __syncthreads();                     // the pass above walked the row element by element
+  for (int i = threadIdx.x * VEC; i < h; i += blockDim.x * VEC) {
+    float z[4], wv[4], res[4];
+    if (VEC == 4) {
+      if (w) load4<TW>(w + i, wv);
+      if (residual) load4<float>(residual + r * h + i, res);
     } else {
-      out32[r * h + i] = z;
+      if (w) wv[0] = to_f32<TW>(w[i]);
+      if (residual) res[0] = residual[r * h + i];
     }
-    if (cast) cast[r * h + i] = from_f32<TA>(z);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      z[j] = ya[i + j];
+      if (w) z[j] = z[j] * rn * wv[j];
+      if (residual) z[j] += res[j];
+    }
+    float* dst = residual ? residual + r * h + i : out32 + r * h + i;
+    if (VEC == 4) { store4<float>(dst, z); if (cast) store4<TA>(cast + r * h + i, z); }
+    else { dst[0] = z[0]; if (cast) cast[r * h + i] = from_f32<TA>(z[0]); }
   }
 }
 
@@ -420,18 +435,23 @@ DINFER_API int dinfer_branch_norm(const void* a, const void* wa, const void* b, 
   if (h <= 0 || num_rows < 0) return refuse(DINFER_BAD_ARGUMENT, "branch_norm: bad sizes rows=%d h=%d", num_rows, h);
   if (!a || (b && (!wa || !wb)) || (!residual && !out32))
     return refuse(DINFER_BAD_ARGUMENT, "branch_norm: a branch without its weight, or no output");
-  const size_t row_bytes = (size_t)h * sizeof(float);
+  const size_t row_bytes = (size_t)h * sizeof(float) * (b ? 2 : 1);
   if (row_bytes > 200 * 1024) return refuse(DINFER_BAD_ARGUMENT, "branch_norm: rows of %d above the limit", h);
   if (num_rows == 0) return 0;
-  int threads = (h + 31) / 32 * 32;
+  const auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  const bool vec4 = h % 4 == 0 && al(a) && al(b) && al(w) && al(residual) && al(out32) && al(cast);
+  int threads = ((vec4 ? h / 4 : h) + 31) / 32 * 32;
   if (threads > 1024) threads = 1024;
   DINFER_DISPATCH_DTYPE(act_dtype, TA,
     DINFER_DISPATCH_DTYPE(w_dtype, TW, {
+      auto k4 = branch_norm_kernel<TA, TW, 4>;
+      auto k1 = branch_norm_kernel<TA, TW, 1>;
+      auto k = vec4 ? k4 : k1;
       if (row_bytes > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(branch_norm_kernel<TA, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)row_bytes);
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)row_bytes);
         if (e != cudaSuccess) return refuse((int)e, "branch_norm: shared memory opt-in failed: %s", cudaGetErrorString(e));
       }
-      launch_pdl(branch_norm_kernel<TA, TW>, dim3(num_rows), dim3(threads), row_bytes, stream, (const TA*)a, (const TW*)wa,
+      launch_pdl(k, dim3(num_rows), dim3(threads), row_bytes, stream, (const TA*)a, (const TW*)wa,
                  (const TA*)b, (const TW*)wb, coef, inner_eps, (const TW*)w, eps, residual, out32, (TA*)cast, h);
       return cuda_status("branch_norm");
     }));

@@ -405,6 +405,7 @@ DINFER_API int dinfer_qk_post(void* qkv, int64_t ld, const int* positions, const
 // per (token, head) of q (H heads of D), k (Hkv of D) and v (Hkv of Dv), in one pass
 //   norm_first:  x <- rms(x) [* w];  x <- rot(x)          (the order of the kernel above)
 //   else:        x <- rot(x);        x <- rms(x) [* w]    (norm = 1; the weights may be null: a norm without a weight)
+// (x = the projection's output, plus `bias` [(H + Hkv) D + Hkv Dv] f32 where the projection has one);
 // q and k written back in place; k and v to the token's slot of a cache [blocks, 2, Hkv, block_size, Dc], whose
 // rows are Dc = max(D, Dv) wide (k in the first D, v in the first Dv elements of a row).
 namespace {
@@ -414,7 +415,8 @@ __global__ void __launch_bounds__(WARPS * 32)
 qkv_post_general_kernel(TA* __restrict__ qkv, int64_t ld, const int* __restrict__ positions,
                         const TW* __restrict__ q_weight, const TW* __restrict__ k_weight, int norm, int norm_first,
                         float eps, const float* __restrict__ cos_sin, int rot, int interleaved, TA* __restrict__ cache,
-                        const int* __restrict__ slots, int block_size, int H, int Hkv, int D, int Dv, int Dc) {
+                        const int* __restrict__ slots, int block_size, int H, int Hkv, int D, int Dv, int Dc,
+                        const float* __restrict__ bias) {
   __shared__ float sm[WARPS][MAX_D];
   pdl_enter();
   const int t = blockIdx.x;
@@ -423,9 +425,12 @@ qkv_post_general_kernel(TA* __restrict__ qkv, int64_t ld, const int* __restrict_
   if (head >= H + 2 * Hkv) return;
   const int kind = head < H ? 0 : (head < H + Hkv ? 1 : 2);
   const int width = kind == 2 ? Dv : D;
-  TA* x = qkv + (int64_t)t * ld + (kind == 2 ? (int64_t)(H + Hkv) * D + (int64_t)(head - H - Hkv) * Dv : (int64_t)head * D);
+  const int64_t at = kind == 2 ? (int64_t)(H + Hkv) * D + (int64_t)(head - H - Hkv) * Dv : (int64_t)head * D;
+  TA* x = qkv + (int64_t)t * ld + at;
   float* xs = sm[warp];
-  for (int e = lane; e < width; e += 32) xs[e] = to_f32<TA>(x[e]);
+  // the projection's bias, where it has one, is added here (rounded as the product's own bias kernel would)
+  for (int e = lane; e < width; e += 32)
+    xs[e] = bias ? to_f32<TA>(from_f32<TA>(to_f32<TA>(x[e]) + bias[at + e])) : to_f32<TA>(x[e]);
   __syncwarp();
   if (kind != 2) {
     const TW* w = kind == 0 ? q_weight : k_weight;
@@ -468,8 +473,8 @@ qkv_post_general_kernel(TA* __restrict__ qkv, int64_t ld, const int* __restrict_
 DINFER_API int dinfer_qkv_post_general(void* qkv, int64_t ld, const int* positions, const void* q_weight,
                                        const void* k_weight, int norm, int norm_first, float eps, const float* cos_sin,
                                        int rot, int interleaved, void* cache, const int* slots, int block_size, int T,
-                                       int H, int Hkv, int D, int Dv, int Dc, int act_dtype, int w_dtype,
-                                       cudaStream_t stream) {
+                                       int H, int Hkv, int D, int Dv, int Dc, const float* bias, int act_dtype,
+                                       int w_dtype, cudaStream_t stream) {
   if (T < 0 || H <= 0 || Hkv < 0 || D <= 0 || Dv <= 0 || Dc < D || Dc < Dv)
     return refuse(DINFER_BAD_ARGUMENT, "qkv_post_general: bad sizes T=%d H=%d Hkv=%d D=%d Dv=%d Dc=%d", T, H, Hkv, D, Dv, Dc);
   if (D > MAX_D || Dv > MAX_D) return refuse(DINFER_BAD_ARGUMENT, "qkv_post_general: head sizes %d / %d above the limit %d", D, Dv, MAX_D);
@@ -483,7 +488,7 @@ DINFER_API int dinfer_qkv_post_general(void* qkv, int64_t ld, const int* positio
     DINFER_DISPATCH_DTYPE(w_dtype, TW, {
       launch_pdl(qkv_post_general_kernel<TA, TW>, grid, dim3(WARPS * 32), 0, stream, (TA*)qkv, ld, positions,
                  (const TW*)q_weight, (const TW*)k_weight, norm, norm_first, eps, cos_sin, rot, interleaved, (TA*)cache,
-                 slots, block_size, H, Hkv, D, Dv, Dc);
+                 slots, block_size, H, Hkv, D, Dv, Dc, bias);
       return cuda_status("qkv_post_general");
     }));
   return 0;

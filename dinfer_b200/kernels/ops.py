@@ -232,11 +232,16 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, b
 def qkv_post_general(qkv: torch.Tensor, positions: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
                      v_dim: int, eps: float, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
                      norm: bool, norm_first: bool, cos_sin: Optional[torch.Tensor], cache: Optional[torch.Tensor],
-                     slots: Optional[torch.Tensor], block_size: int, interleaved: bool = False) -> None:
+                     slots: Optional[torch.Tensor], block_size: int, interleaved: bool = False,
+                     bias: Optional[torch.Tensor] = None) -> None:
     """The general q/k/v post-processing: per-head RMS norm of q and k (``norm``; the weights may be None: a norm
     without a weight) before or behind (``norm_first``) the rotation, q and k written back in place, k and v (v of
-    width ``v_dim``) into a paged cache whose rows are ``max(head_dim, v_dim)`` wide."""
-    require_cuda(qkv, positions, q_weight, k_weight, cos_sin, cache, slots)
+    width ``v_dim``) into a paged cache whose rows are ``max(head_dim, v_dim)`` wide.  ``bias``: f32, one per column of
+    the q, k, v projections, added first (a projection whose bias has no kernel of its own)."""
+    require_cuda(qkv, positions, q_weight, k_weight, cos_sin, cache, slots, bias)
+    if bias is not None and (bias.dtype != torch.float32 or not bias.is_contiguous()
+                             or bias.numel() != (num_heads + num_kv_heads) * head_dim + num_kv_heads * v_dim):
+        raise KernelError("qkv_post_general: bias f32 [(H + Hkv) * D + Hkv * Dv]")
     _rows_contiguous(qkv, "qkv_post_general")
     T = qkv.shape[0]
     row = max(head_dim, v_dim)
@@ -259,10 +264,10 @@ def qkv_post_general(qkv: torch.Tensor, positions: torch.Tensor, num_heads: int,
                               f"activations' dtype, contiguous; slots int32 [T]")
     lib, f = _fn("qk_post", "dinfer_qkv_post_general",
                  [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_int,
-                  c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+                  c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p])
     check(lib, f(ptr(qkv), qkv.stride(0), ptr(positions), ptr(q_weight), ptr(k_weight), int(bool(norm)),
                  int(bool(norm_first)), float(eps), ptr(cos_sin), rot, int(bool(interleaved)), ptr(cache), ptr(slots),
-                 block_size, T, num_heads, num_kv_heads, head_dim, v_dim, row, dtype_code(qkv.dtype), dtype_code(w_dt),
+                 block_size, T, num_heads, num_kv_heads, head_dim, v_dim, row, ptr(bias), dtype_code(qkv.dtype), dtype_code(w_dt),
                  stream_handle()), "qkv_post_general")
 
 

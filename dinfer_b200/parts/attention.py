@@ -92,7 +92,9 @@ class GQAttention(Mixer):
         if self.bias:
             qkv_bias = torch.cat([tensors[self._bias_name(x)].to(dt) for x in ("q", "k", "v")])
             o_bias = tensors[self._bias_name("o")]
-        self.qkv = Linear(torch.cat([q.to(dt), k.to(dt), v.to(dt)], dim=0), qkv_bias)
+        # with the general q/k/v kernel the projection's bias is added there, not by a kernel of its own
+        self.qkv_bias32 = qkv_bias.float().contiguous() if (self.general and qkv_bias is not None) else None
+        self.qkv = Linear(torch.cat([q.to(dt), k.to(dt), v.to(dt)], dim=0), None if self.general else qkv_bias)
         self.o = Linear(tensors[self.names["o"]], o_bias)
         if self.qk_norm and self.norm_weight:
             self.q_norm_w = tensors[self.names["qn"]].contiguous()
@@ -131,7 +133,7 @@ class GQAttention(Mixer):
                                           "need a position encoding the q/k kernel applies")
             ops.qkv_post_general(qkv, ctx.positions, H, Hkv, D, self.Dv, self.eps, self.q_norm_w, self.k_norm_w,
                                  self.qk_norm, not self.norm_after, table, kv, g.slot_mapping, g.block_size,
-                                 interleaved=getattr(self.position, "interleaved", False))
+                                 interleaved=getattr(self.position, "interleaved", False), bias=self.qkv_bias32)
         elif self.position.fused:
             ops.qk_post(qkv, ctx.positions, H, Hkv, D, self.eps, self.q_norm_w, self.k_norm_w, table,
                         kv, g.slot_mapping, g.block_size, interleaved=getattr(self.position, "interleaved", False))
