@@ -419,7 +419,7 @@ DINFER_API int dinfer_delta_prep(const void* P, int64_t ldp, int cq, int ck, int
 DINFER_API int dinfer_delta_recurrence(const float* qn, const float* kn, const float* vv, const float* beta,
                                        const float* decay, float* state, int64_t state_stride, const int* cu,
                                        const int* slots, const int* fresh, float* out, int B, int H, int G, int dk,
-                                       int dv, int per_channel, cudaStream_t stream) {
+                                       int dv, int per_channel, int force_widen, cudaStream_t stream) {
   if (B <= 0 || H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || H > 65535 || B > 65535)
     return refuse(DINFER_BAD_ARGUMENT, "delta_recurrence: bad sizes B=%d H=%d G=%d dk=%d dv=%d", B, H, G, dk, dv);
   // key widths that split evenly over the lanes of a column (and rows that cp.async can fetch in 16-byte pieces): the
@@ -439,11 +439,34 @@ DINFER_API int dinfer_delta_recurrence(const float* qn, const float* kn, const f
                kn, vv, beta, decay, state, state_stride, cu, slots, fresh, out, H, G, dv, per_channel);             \
     return cuda_status("delta_recurrence");                                                                         \
   } while (0)
-    if (dk == 16) GO_REG(16, 1);
-    if (dk == 32) GO_REG(16, 2);
-    if (dk == 64) GO_REG(16, 4);
-    if (dk == 128) GO_REG(16, 8);
-    GO_REG(32, 8);
+    // How many lanes share a column.  The token loop is a chain, so a warp issues an instruction every few cycles at
+    // best: the device is busy only with several warps on every scheduler.  With few (request, head) pairs the
+    // columns are therefore shared by two or four times the lanes (a lane owns 8 or 4 rows instead of 16: more
+    // warps, each with a shorter step), as far as that is needed to put about three warps on every scheduler.
+    static int sms = 0;
+    if (!sms) { int d = 0; cudaGetDevice(&d); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, d); if (sms <= 0) sms = 148; }
+    const int base = dk == 256 ? 8 : dk / 16;
+    const int64_t cols = (int64_t)B * H * dv;
+    int widen = 1;
+    while (widen < 4 && cols * base * widen / 32 < (int64_t)3 * 4 * sms) widen *= 2;
+    if (force_widen == 1 || force_widen == 2 || force_widen == 4) widen = force_widen;   // for tests: 0 lets the sizes decide
+    if (dk == 256 && widen == 4) widen = 2;
+    switch (dk * 8 + widen) {
+      case 16 * 8 + 1: GO_REG(16, 1);
+      case 16 * 8 + 2: GO_REG(8, 2);
+      case 16 * 8 + 4: GO_REG(4, 4);
+      case 32 * 8 + 1: GO_REG(16, 2);
+      case 32 * 8 + 2: GO_REG(8, 4);
+      case 32 * 8 + 4: GO_REG(4, 8);
+      case 64 * 8 + 1: GO_REG(16, 4);
+      case 64 * 8 + 2: GO_REG(8, 8);
+      case 64 * 8 + 4: GO_REG(4, 16);
+      case 128 * 8 + 1: GO_REG(16, 8);
+      case 128 * 8 + 2: GO_REG(8, 16);
+      case 128 * 8 + 4: GO_REG(4, 32);
+      case 256 * 8 + 1: GO_REG(32, 8);
+      default: GO_REG(16, 16);
+    }
 #undef GO_REG
   }
   // lanes that share a column: enough that a lane owns about 16 rows, fewer for a narrow state

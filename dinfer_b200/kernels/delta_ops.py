@@ -60,9 +60,11 @@ def prep(P: torch.Tensor, cols: Tuple[int, int, int, int], A: torch.Tensor, conv
 
 def recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor,
                state: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor, fresh: torch.Tensor,
-               per_channel: bool) -> torch.Tensor:
+               per_channel: bool, widen: int = 0) -> torch.Tensor:
     """Token by token per request and head: ``S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q``, S [dk, dv]
-    of head h at ``state[slot, h * dk * dv:]`` (zero for a fresh request), carried in place.  Returns o f32 [T, H, dv]."""
+    of head h at ``state[slot, h * dk * dv:]`` (zero for a fresh request), carried in place.  Returns o f32 [T, H, dv].
+    ``widen`` (1, 2, 4; 0: the sizes decide): how far a column's rows are spread over more lanes than 16 rows a lane
+    would need, which only changes the order of the sums."""
     require_cuda(q, k, v, beta, decay, state, cu_seqlens, slots, fresh)
     _ints(cu_seqlens, slots, fresh)
     T, G, dk = q.shape
@@ -77,10 +79,10 @@ def recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Te
         return out
     lib, f = _fn("delta_rule", "dinfer_delta_recurrence",
                  [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
-                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
     check(lib, f(ptr(q), ptr(k), ptr(v), ptr(beta), ptr(decay), ptr(state), state.stride(0), ptr(cu_seqlens),
                  ptr(slots), ptr(fresh), ptr(out), cu_seqlens.numel() - 1, H, G, dk, dv, int(bool(per_channel)),
-                 stream_handle()), "delta_recurrence")
+                 int(widen), stream_handle()), "delta_recurrence")
     return out
 
 

@@ -230,14 +230,16 @@ def test_delta_recurrence(H_, G, dk, dv, per_channel):
     want = torch.cat(want)
     assert torch.allclose(out.cpu().to(F64), want, rtol=2e-5, atol=2e-5), float((out.cpu() - want).abs().max())
     assert torch.allclose(state[1, :H_ * dk * dv].cpu().to(F64).reshape(H_, dk, dv), S, rtol=2e-5, atol=2e-5)
-    # request 0 again in portions, in slot 1 (used by request 2 above) and marked fresh only in its first step
-    got, at = [], 0
-    for n in (1, 2, 1, 9, 2, 22):
-        s = slice(at, at + n)
-        got.append(delta_ops.recurrence(f(q[s]), f(k[s]), f(v[s]), f(beta[s]), f(decay[s].reshape(n, -1)), state,
-                                        i32([0, n]), i32([1]), i32([int(at == 0)]), per_channel))
-        at += n
-    assert torch.allclose(torch.cat(got), out[:37], rtol=1e-5, atol=1e-6)
+    # request 0 again in portions, in slot 1 (used by request 2 above) and marked fresh only in its first step; with a
+    # column's rows spread over 1, 2 or 4 times the lanes (what the kernel otherwise chooses by the batch's size)
+    for widen in (0, 1, 2, 4):
+        got, at = [], 0
+        for n in (1, 2, 1, 9, 2, 22):
+            s = slice(at, at + n)
+            got.append(delta_ops.recurrence(f(q[s]), f(k[s]), f(v[s]), f(beta[s]), f(decay[s].reshape(n, -1)), state,
+                                            i32([0, n]), i32([1]), i32([int(at == 0)]), per_channel, widen=widen))
+            at += n
+        assert torch.allclose(torch.cat(got), out[:37], rtol=1e-5, atol=2e-6), widen
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
