@@ -440,15 +440,17 @@ DINFER_API int dinfer_delta_recurrence(const float* qn, const float* kn, const f
     return cuda_status("delta_recurrence");                                                                         \
   } while (0)
     // How many lanes share a column.  The token loop is a chain, so a warp issues an instruction every few cycles at
-    // best: the device is busy only with several warps on every scheduler.  With few (request, head) pairs the
-    // columns are therefore shared by two or four times the lanes (a lane owns 8 or 4 rows instead of 16: more
-    // warps, each with a shorter step), as far as that is needed to put about three warps on every scheduler.
+    // best: the device is busy only with several warps on every scheduler.  With few (request, head) pairs and a
+    // narrow key the columns are therefore shared by two or four times the lanes (a lane owns 8 or 4 rows instead of
+    // 16: more warps, each with a shorter step), up to 8 lanes a column: beyond that the longer exchange between the
+    // lanes costs more than the shorter step gains (measured: 128 key channels on 8 / 16 / 32 lanes 540 / 600 / 600 us
+    // for 2048 tokens of 16 heads, 64 key channels on 4 / 8 / 16 lanes 495 / 455 / 405 us).
     static int sms = 0;
     if (!sms) { int d = 0; cudaGetDevice(&d); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, d); if (sms <= 0) sms = 148; }
     const int base = dk == 256 ? 8 : dk / 16;
     const int64_t cols = (int64_t)B * H * dv;
     int widen = 1;
-    while (widen < 4 && cols * base * widen / 32 < (int64_t)3 * 4 * sms) widen *= 2;
+    while (widen < 4 && base * widen * 2 <= 8 && cols * base * widen / 32 < (int64_t)3 * 4 * sms) widen *= 2;
     if (force_widen == 1 || force_widen == 2 || force_widen == 4) widen = force_widen;   // for tests: 0 lets the sizes decide
     if (dk == 256 && widen == 4) widen = 2;
     switch (dk * 8 + widen) {
