@@ -4,7 +4,7 @@
 //   delta_prep        per token: short convolution (+ silu) of the q / k / v projections, reading what the
 //                     convolution needs from before the step out of the request's state; q and k made unit vectors
 //                     per head (q also times dk^-1/2); beta = sigmoid(b); decay g = exp(-exp(A_log) * softplus(a + dt_bias)),
-//                     one per head or one per head and key channel.  All results 32-bit.
+//                     one per head or one per head and key channel, handed on as g - 1 = expm1(...).  All results 32-bit.
 //   delta_conv_state  per request: the step's last (taps - 1) convolution inputs become the state's.
 //   delta_recurrence  per (request, head, group of value columns), token by token:
 //                         S <- g * S;  u = beta * (v - S^T k);  S <- S + k u^T;  o = S^T q
@@ -14,6 +14,11 @@
 //   delta_post        per (token, head): o / rms(o) * w * act(gate), rounded to the activation type.
 //
 // A request whose `fresh` flag is set starts from a zero state (nothing is read from its slot).
+//
+// Why g - 1: a slow decay is a g just below one, where 32-bit numbers lie 6e-8 apart; a head whose g hardly changes from
+// token to token would multiply its state by the same rounding error every time, and a thousand tokens on the state's
+// oldest content is off by several 1e-5.  g - 1 = expm1(-x) keeps the decay's own digits, and S g = fma(S, g - 1, S)
+// rounds once, without a bias.
 #include "common.cuh"
 
 using namespace dinfer;
@@ -97,7 +102,7 @@ delta_prep_kernel(const TA* __restrict__ P, int64_t ldp, int cq, int ck, int cv,
   for (int c = job * PREP_CHUNK + threadIdx.x; c < min(nd, (job + 1) * PREP_CHUNK); c += blockDim.x) {
     const int h = per_channel ? c / dk : c;
     const float a = to_f32<TA>(A[(int64_t)t * lda + c]) + dt_bias[c];
-    decay[(int64_t)t * nd + c] = expf(-expf(A_log[h]) * softplus_f(a));
+    decay[(int64_t)t * nd + c] = expm1f(-expf(A_log[h]) * softplus_f(a));       // g - 1, see the head of the file
   }
 }
 
@@ -186,7 +191,8 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
       const float* gc = sg + j * dk;
       float read = 0.f;
       for (int i = sub; i < dk; i += LPC) {
-        const float s = S[i * SB + lc] * (per_channel ? gc[i] : gs);
+        const float s0 = S[i * SB + lc];
+        const float s = fmaf(s0, per_channel ? gc[i] : gs, s0);                // S g = S + S (g - 1)
         S[i * SB + lc] = s;
         read = fmaf(s, k[i], read);
       }
@@ -306,7 +312,7 @@ delta_recurrence_reg_kernel(const float* __restrict__ qn, const float* __restric
       const float4* k4 = reinterpret_cast<const float4*>(sk + j * DK);
       const float4* q4 = reinterpret_cast<const float4*>(sq + j * DK);
       const float4* g4 = reinterpret_cast<const float4*>(sg + j * DK);
-      const float gs = per_channel ? 1.f : sg[j];
+      const float gs = per_channel ? 0.f : sg[j];
       float kr[R];
       float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
 #pragma unroll
@@ -315,7 +321,10 @@ delta_recurrence_reg_kernel(const float* __restrict__ qn, const float* __restric
         float4 gg = make_float4(gs, gs, gs, gs);
         if (per_channel) gg = g4[m * LPC + sub];
         kr[m * 4] = kk.x; kr[m * 4 + 1] = kk.y; kr[m * 4 + 2] = kk.z; kr[m * 4 + 3] = kk.w;
-        S[m * 4] *= gg.x; S[m * 4 + 1] *= gg.y; S[m * 4 + 2] *= gg.z; S[m * 4 + 3] *= gg.w;
+        S[m * 4] = fmaf(S[m * 4], gg.x, S[m * 4]);             // S g = S + S (g - 1)
+        S[m * 4 + 1] = fmaf(S[m * 4 + 1], gg.y, S[m * 4 + 1]);
+        S[m * 4 + 2] = fmaf(S[m * 4 + 2], gg.z, S[m * 4 + 2]);
+        S[m * 4 + 3] = fmaf(S[m * 4 + 3], gg.w, S[m * 4 + 3]);
         r0 = fmaf(S[m * 4], kk.x, r0);
         r1 = fmaf(S[m * 4 + 1], kk.y, r1);
         r2 = fmaf(S[m * 4 + 2], kk.z, r2);

@@ -23,7 +23,8 @@ def prep(P: torch.Tensor, cols: Tuple[int, int, int, int], A: torch.Tensor, conv
     [T, H] or [T, H * dk]: the short convolutions with silu (what lies before the step comes from the requests'
     state, whose convolution history is brought up to date afterwards), unit q and k, beta, decay.  ``state``
     [slots, S + (taps - 1) * C] f32: the matrix S of every head, then the convolution history from ``hist_offset``.
-    Returns f32 (q [T, G, dk], k [T, G, dk], v [T, H, dv], beta [T, H], decay [T, H] or [T, H, dk])."""
+    Returns f32 (q [T, G, dk], k [T, G, dk], v [T, H, dv], beta [T, H], decay [T, H] or [T, H, dk]); the decay comes as
+    ``g - 1`` (``expm1`` of its exponent), which keeps the digits of a g just below one."""
     require_cuda(P, A, conv_w, A_log, dt_bias, state, cu_seqlens, slots, fresh)
     _rows_contiguous(P, "delta prep P")
     _rows_contiguous(A, "delta prep A")
@@ -61,7 +62,8 @@ def prep(P: torch.Tensor, cols: Tuple[int, int, int, int], A: torch.Tensor, conv
 def recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor,
                state: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor, fresh: torch.Tensor,
                per_channel: bool, widen: int = 0) -> torch.Tensor:
-    """Token by token per request and head: ``S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q``, S [dk, dv]
+    """Token by token per request and head: ``S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q`` (``decay``
+    holds ``g - 1``, as ``prep`` makes it), S [dk, dv]
     of head h at ``state[slot, h * dk * dv:]`` (zero for a fresh request), carried in place.  Returns o f32 [T, H, dv].
     ``widen`` (1, 2, 4; 0: the sizes decide): how far a column's rows are spread over more lanes than 16 rows a lane
     would need, which only changes the order of the sums."""

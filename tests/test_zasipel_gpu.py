@@ -219,7 +219,7 @@ def test_delta_recurrence(H_, G, dk, dv, per_channel):
     f = lambda t: dev(t, torch.float32)
     state = torch.full((5, H_ * dk * dv + 3), float("nan"), dtype=torch.float32, device="cuda")
     cu = i32([0, 37, 38, 56])
-    out = delta_ops.recurrence(f(q), f(k), f(v), f(beta), f(decay.reshape(T, -1)), state, cu, i32([3, 0, 1]), i32([1, 1, 1]), per_channel)
+    out = delta_ops.recurrence(f(q), f(k), f(v), f(beta), f(decay.reshape(T, -1) - 1), state, cu, i32([3, 0, 1]), i32([1, 1, 1]), per_channel)
     rep = H_ // G
     want, at = [], 0
     for n in lens:
@@ -236,7 +236,7 @@ def test_delta_recurrence(H_, G, dk, dv, per_channel):
         got, at = [], 0
         for n in (1, 2, 1, 9, 2, 22):
             s = slice(at, at + n)
-            got.append(delta_ops.recurrence(f(q[s]), f(k[s]), f(v[s]), f(beta[s]), f(decay[s].reshape(n, -1)), state,
+            got.append(delta_ops.recurrence(f(q[s]), f(k[s]), f(v[s]), f(beta[s]), f(decay[s].reshape(n, -1) - 1), state,
                                             i32([0, n]), i32([1]), i32([int(at == 0)]), per_channel, widen=widen))
             at += n
         assert torch.allclose(torch.cat(got), out[:37], rtol=1e-5, atol=2e-6), widen
@@ -283,7 +283,7 @@ def test_delta_prep_and_post(dtype, per_channel, taps, H_, G, dk, dv):
         a = A_in[r].to(F64) + dt_bias.to(F64)
         decay = torch.exp(-torch.exp(A_log.to(F64)).repeat_interleave(dk if per_channel else 1) * P.softplus(a))
         want = [P.unit(y["q"].reshape(n, G, dk)) * dk ** -0.5, P.unit(y["k"].reshape(n, G, dk)), y["v"].reshape(n, H_, dv),
-                torch.sigmoid(x[:, C_ + 5:]), decay]
+                torch.sigmoid(x[:, C_ + 5:]), decay - 1]              # the kernel hands the decay on as g - 1
         for j, w in enumerate(want):
             have = torch.cat([piece[j] for piece in got[r]])
             assert torch.allclose(have, w, **tol), (r, j, float((have - w).abs().max()))
@@ -312,7 +312,7 @@ def test_delta_rule_remembers_a_far_token():
     q[T - 1] = k[7] + 0.0
     f = lambda t: dev(t, torch.float32)
     state = torch.zeros((1, dk * dv), dtype=torch.float32, device="cuda")
-    out = delta_ops.recurrence(f(q), f(k), f(v), f(beta), f(decay), state, i32([0, T]), i32([0]), i32([1]), False)
+    out = delta_ops.recurrence(f(q), f(k), f(v), f(beta), f(decay - 1), state, i32([0, T]), i32([0]), i32([1]), False)
     want, _ = P.delta_rule(q, k, v, beta, decay)
     assert float(want[-1].abs().min()) > 3.0
     assert torch.allclose(out.cpu().to(F64), want, rtol=1e-4, atol=1e-4)
