@@ -112,3 +112,29 @@ def test_plain_window_sink_and_history():
     ya, ha = P.short_conv(x[:2], w)
     yb, hb = P.short_conv(x[2:], w, ha)
     assert torch.allclose(torch.cat([ya, yb]), y) and torch.equal(hb, hist) and torch.equal(hist, x[3:])
+
+
+def test_random_model_folder(tmp_path):
+    """The random-weights mode writes a folder the engine's own reader takes: every declared tensor, the experts'
+    tables as int32 with rows of different entries."""
+    from dinfer_b200.weights.loader import SafetensorsSource, verify
+    from dinfer_b200.weights.random_init import write_random_model
+    d = write_random_model(str(tmp_path / "m"), C.ZASIPEL_C, seed=3)
+    src = SafetensorsSource(d)
+    try:
+        assert verify(src, model_declarations(C.ZASIPEL_C)) == []
+        table = src.get("l1.mlp.table")
+        assert table.dtype == torch.int32 and tuple(table.shape) == (331, 1) and int(table.max()) < 7
+        assert src.dtype("l0.mix.right.q") == torch.bfloat16
+    finally:
+        src.close()
+    # a file whose thin middles disagree with one another is refused when the part binds them
+    from dinfer_b200.parts.base import BuildEnv
+    from dinfer_b200.parts.delta_rule import GatedDelta
+    part = GatedDelta({"num_heads": 2, "num_kv_heads": 1, "key_dim": 4, "value_dim": 4, "conv": 2, "eps": 1e-5,
+                       "decay": "channel", "gate": "sigmoid", "decay_rank": -1, "gate_rank": -1},
+                      BuildEnv(torch.device("cpu"), torch.float32, 8, 16), "")
+    W = {t.name: torch.zeros([3 if n < 0 else n for n in t.shape]) for t in part.declare()}
+    W["a2"] = torch.zeros(8, 5)
+    with pytest.raises(ValueError, match="thin middle"):
+        part.bind(W)
