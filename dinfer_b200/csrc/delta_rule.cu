@@ -62,14 +62,22 @@ delta_prep_kernel(const TA* __restrict__ P, int64_t ldp, int cq, int ck, int cv,
   const float* hb = hist + (int64_t)slots[b] * hist_stride;
   const int nq = G * dk, nv = H * dv, C = 2 * nq + nv;
   const int nvb = (nv + PREP_CHUNK - 1) / PREP_CHUNK;
+  const TA* row = P + (int64_t)t * ldp;                    // this token's projections; the token before lies ldp back
+  const bool inside = i >= taps - 1;                       // every tap falls into the step's own tokens (the usual case)
   auto conv = [&](int c) {                                 // channel c of q | k | v: the convolution, then silu
     const int col = c < nq ? cq + c : (c < 2 * nq ? ck + c - nq : cv + c - 2 * nq);
+    const float* w = conv_w + c * taps + taps - 1;         // w[-d] weighs the token d back
+    const TA* x = row + col;
     float acc = 0.f;
-    for (int d = 0; d < taps; ++d) {                       // d tokens back
-      float x = 0.f;
-      if (i - d >= 0) x = to_f32<TA>(P[(int64_t)(t - d) * ldp + col]);
-      else if (have_hist) x = hb[(int64_t)(taps - 1 + i - d) * C + c];
-      acc = fmaf(conv_w[(int64_t)c * taps + taps - 1 - d], x, acc);
+    if (inside) {
+      for (int d = 0; d < taps; ++d, x -= ldp) acc = fmaf(w[-d], to_f32<TA>(*x), acc);
+    } else {
+      for (int d = 0; d < taps; ++d) {                     // d tokens back: from the step, or from the request's history
+        float v = 0.f;
+        if (i - d >= 0) v = to_f32<TA>(x[-(int64_t)d * ldp]);
+        else if (have_hist) v = hb[(taps - 1 + i - d) * C + c];
+        acc = fmaf(w[-d], v, acc);
+      }
     }
     return silu_f(acc);
   };
