@@ -360,9 +360,9 @@ DINFER_API int dinfer_scaled_add(float* residual, const void* d1, const void* s1
 // All of it in 32-bit, the row kept in shared memory.  One block per row.
 namespace {
 
-template <typename TA, typename TW, int VEC>
+template <typename TIN, typename TA, typename TW, int VEC>
 __global__ void __launch_bounds__(1024)
-branch_norm_kernel(const TA* __restrict__ a, const TW* __restrict__ wa, const TA* __restrict__ b,
+branch_norm_kernel(const TIN* __restrict__ a, const TW* __restrict__ wa, const TIN* __restrict__ b,
                    const TW* __restrict__ wb, float coef, float inner_eps, const TW* __restrict__ w, float eps,
                    float* __restrict__ residual, float* __restrict__ out32, TA* __restrict__ cast, int h) {
   extern __shared__ __align__(16) float rows_sm[];        // the row of a, and of b behind it: each is read from memory once
@@ -371,13 +371,13 @@ branch_norm_kernel(const TA* __restrict__ a, const TW* __restrict__ wa, const TA
   float* yb = rows_sm + h;
   pdl_enter();
   const int64_t r = blockIdx.x;
-  const TA* pa = a + r * h;
-  const TA* pb = b ? b + r * h : nullptr;
+  const TIN* pa = a + r * h;
+  const TIN* pb = b ? b + r * h : nullptr;
   float sa = 0.f, sb = 0.f;
   for (int i = threadIdx.x * VEC; i < h; i += blockDim.x * VEC) {
     float x[4], y[4];
-    if (VEC == 4) { load4<TA>(pa + i, x); if (pb) load4<TA>(pb + i, y); }
-    else { x[0] = to_f32<TA>(pa[i]); if (pb) y[0] = to_f32<TA>(pb[i]); }
+    if (VEC == 4) { load4<TIN>(pa + i, x); if (pb) load4<TIN>(pb + i, y); }
+    else { x[0] = to_f32<TIN>(pa[i]); if (pb) y[0] = to_f32<TIN>(pb[i]); }
 #pragma unroll
     for (int j = 0; j < VEC; ++j) {
       ya[i + j] = x[j];
@@ -426,12 +426,12 @@ branch_norm_kernel(const TA* __restrict__ a, const TW* __restrict__ wa, const TA
 
 }  // namespace
 
-// a, b [num_rows, h] act dtype (b null: one branch); wa, wb inner weights [h] (wa null: no inner norm); w the outer
+// a, b [num_rows, h] of in_dtype (b null: one branch); wa, wb inner weights [h] (wa null: no inner norm); w the outer
 // weight [h] (null: none); residual f32 [num_rows, h] updated in place, or null with out32 f32 [num_rows, h];
 // cast [num_rows, h] act dtype or null.
 DINFER_API int dinfer_branch_norm(const void* a, const void* wa, const void* b, const void* wb, float coef,
                                   float inner_eps, const void* w, float eps, float* residual, float* out32, void* cast,
-                                  int num_rows, int h, int act_dtype, int w_dtype, cudaStream_t stream) {
+                                  int num_rows, int h, int in_dtype, int act_dtype, int w_dtype, cudaStream_t stream) {
   if (h <= 0 || num_rows < 0) return refuse(DINFER_BAD_ARGUMENT, "branch_norm: bad sizes rows=%d h=%d", num_rows, h);
   if (!a || (b && (!wa || !wb)) || (!residual && !out32))
     return refuse(DINFER_BAD_ARGUMENT, "branch_norm: a branch without its weight, or no output");
@@ -442,18 +442,19 @@ DINFER_API int dinfer_branch_norm(const void* a, const void* wa, const void* b, 
   const bool vec4 = h % 4 == 0 && al(a) && al(b) && al(w) && al(residual) && al(out32) && al(cast);
   int threads = ((vec4 ? h / 4 : h) + 31) / 32 * 32;
   if (threads > 1024) threads = 1024;
-  DINFER_DISPATCH_DTYPE(act_dtype, TA,
+  DINFER_DISPATCH_DTYPE(in_dtype, TIN,
+   DINFER_DISPATCH_DTYPE(act_dtype, TA,
     DINFER_DISPATCH_DTYPE(w_dtype, TW, {
-      auto k4 = branch_norm_kernel<TA, TW, 4>;
-      auto k1 = branch_norm_kernel<TA, TW, 1>;
+      auto k4 = branch_norm_kernel<TIN, TA, TW, 4>;
+      auto k1 = branch_norm_kernel<TIN, TA, TW, 1>;
       auto k = vec4 ? k4 : k1;
       if (row_bytes > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)row_bytes);
         if (e != cudaSuccess) return refuse((int)e, "branch_norm: shared memory opt-in failed: %s", cudaGetErrorString(e));
       }
-      launch_pdl(k, dim3(num_rows), dim3(threads), row_bytes, stream, (const TA*)a, (const TW*)wa,
-                 (const TA*)b, (const TW*)wb, coef, inner_eps, (const TW*)w, eps, residual, out32, (TA*)cast, h);
+      launch_pdl(k, dim3(num_rows), dim3(threads), row_bytes, stream, (const TIN*)a, (const TW*)wa,
+                 (const TIN*)b, (const TW*)wb, coef, inner_eps, (const TW*)w, eps, residual, out32, (TA*)cast, h);
       return cuda_status("branch_norm");
-    }));
+    })));
   return 0;
 }

@@ -91,17 +91,17 @@ def recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Te
 def post(o: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, eps: float, sigmoid_gate: bool,
          out: torch.Tensor) -> torch.Tensor:
     """``out[t, h] = o[t, h] / rms(o[t, h]) * weight * act(gate[t, h])`` with act = sigmoid or silu; o f32 [T, H, dv],
-    gate and out [T, H * dv] of the activations' dtype (views with a row stride are fine)."""
+    gate [T, H * dv] (its own dtype) and out [T, H * dv] of the activations' dtype (views with a row stride are fine)."""
     require_cuda(o, weight, gate, out)
     T, H, dv = o.shape
     _rows_contiguous(gate, "delta post gate")
     _rows_contiguous(out, "delta post out")
     if o.dtype != torch.float32 or not o.is_contiguous() or weight.dtype != torch.float32 or weight.numel() != dv \
-            or gate.dtype != out.dtype or gate.shape[0] != T or gate.shape[1] < H * dv or tuple(out.shape) != (T, H * dv):
+            or gate.shape[0] != T or gate.shape[1] < H * dv or tuple(out.shape) != (T, H * dv):
         raise KernelError("delta post: o f32 [T, H, dv], weight f32 [dv], gate / out [T, H * dv]")
     lib, f = _fn("delta_rule", "dinfer_delta_post",
                  [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_float, c_int, c_int,
-                  c_void_p])
+                  c_int, c_void_p])
     check(lib, f(ptr(o), ptr(weight), ptr(gate), gate.stride(0), ptr(out), out.stride(0), T, H, dv, float(eps),
-                 int(bool(sigmoid_gate)), dtype_code(out.dtype), stream_handle()), "delta_post")
+                 int(bool(sigmoid_gate)), dtype_code(gate.dtype), dtype_code(out.dtype), stream_handle()), "delta_post")
     return out

@@ -275,7 +275,8 @@ def branch_norm(a: torch.Tensor, weight: Optional[torch.Tensor], eps: float, res
                 out32: Optional[torch.Tensor] = None, cast: Optional[torch.Tensor] = None,
                 inner=None, b: Optional[torch.Tensor] = None, coef: float = 1.0, inner_eps: float = 0.0):
     """A branch output normed before it joins the residual stream: ``residual += rms(y) * weight`` (or ``out32 = ...``
-    without a residual; ``weight`` None: no outer norm), ``cast = T(residual)`` on the way.  ``y = a``, or with
+    without a residual; ``weight`` None: no outer norm), ``cast = T(residual)`` on the way (T the cast's own dtype;
+    the branches may be wider: 32-bit outputs of their last products).  ``y = a``, or with
     ``inner = (w_a, w_b)``: ``y = coef * (rms(a) * w_a + rms(b) * w_b)`` (``b`` None: one branch).  32-bit throughout."""
     require_cuda(a, b, weight, residual, out32, cast)
     R, h = a.shape
@@ -286,14 +287,16 @@ def branch_norm(a: torch.Tensor, weight: Optional[torch.Tensor], eps: float, res
         _opt_vec(w, h, w_dt, "branch_norm: a weight")
     if not a.is_contiguous() or (b is not None and (b.shape != a.shape or b.dtype != a.dtype or not b.is_contiguous())):
         raise KernelError("branch_norm: branches [R, h] contiguous of one dtype")
-    for t, dt in ((residual, torch.float32), (out32, torch.float32), (cast, a.dtype)):
-        if t is not None and (tuple(t.shape) != (R, h) or t.dtype != dt or not t.is_contiguous()):
-            raise KernelError("branch_norm: residual / out32 f32 [R, h], cast [R, h] of the branches' dtype, contiguous")
+    for t in (residual, out32, cast):
+        if t is not None and (tuple(t.shape) != (R, h) or not t.is_contiguous()
+                              or (t is not cast and t.dtype != torch.float32)):
+            raise KernelError("branch_norm: residual / out32 f32 [R, h], cast [R, h], contiguous")
     lib, f = _fn("norm", "dinfer_branch_norm",
                  [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_float, c_void_p, c_void_p,
-                  c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
     check(lib, f(ptr(a), ptr(wa), ptr(b), ptr(wb), float(coef), float(inner_eps), ptr(weight), float(eps),
-                 ptr(residual), ptr(out32), ptr(cast), R, h, dtype_code(a.dtype), dtype_code(w_dt), stream_handle()),
+                 ptr(residual), ptr(out32), ptr(cast), R, h, dtype_code(a.dtype),
+                 dtype_code(cast.dtype if cast is not None else a.dtype), dtype_code(w_dt), stream_handle()),
           "branch_norm")
     return residual if residual is not None else out32
 

@@ -24,13 +24,13 @@ def _window_attention(a: WindowAttentionSizes, cfg: ZasipelConfig, at: str) -> P
     return PartSpec("gqa_attention", {
         "num_heads": a.heads, "num_kv_heads": a.kv_heads, "head_dim": a.dim, "v_dim": a.vdim, "scale": a.scale,
         "window": a.window, "sink": True, "qk_norm": True, "qk_norm_order": "after", "qk_norm_weight": False,
-        "eps": cfg.norm_eps, "bias": True, "bias_suffix": ".b", "position": position,
+        "eps": cfg.norm_eps, "bias": True, "bias_suffix": ".b", "position": position, "out_float32": True,
         "q_proj": at + "q", "k_proj": at + "k", "v_proj": at + "v", "o_proj": at + "o"})
 
 
 def _delta_rule(r: DeltaRuleSizes, cfg: ZasipelConfig, at: str, channel: bool) -> PartSpec:
     p = {"num_heads": r.heads, "num_kv_heads": r.kv_heads, "key_dim": r.dim, "value_dim": r.vdim, "conv": r.conv,
-         "eps": cfg.norm_eps, "q_proj": at + "q", "k_proj": at + "k", "v_proj": at + "v", "beta_proj": at + "b",
+         "eps": cfg.norm_eps, "out_float32": True, "q_proj": at + "q", "k_proj": at + "k", "v_proj": at + "v", "beta_proj": at + "b",
          "A_log": at + "A_log", "dt_bias": at + "dt_bias", "norm": at + "norm", "o_proj": at + "o"}
     if channel:
         p.update(decay="channel", gate="sigmoid", decay_rank=r.decay_rank, gate_rank=r.gate_rank,

@@ -30,7 +30,8 @@ class GQAttention(Mixer):
     names ``q_proj``, ``k_proj``, ``v_proj``, ``o_proj``, ``q_norm``, ``k_norm`` (after the prefix).  Further:
     ``v_dim`` (the values' width where it differs from ``head_dim``), ``qk_norm_order`` ("before" the rotation, the
     default, or "after" it), ``qk_norm_weight`` (False: the head norm has no weight), ``sink`` (the softmax has one
-    more term of score 0 that carries no value: ``p_j = exp(s_j) / (1 + sum exp(s_j))``)."""
+    more term of score 0 that carries no value: ``p_j = exp(s_j) / (1 + sum exp(s_j))``), ``out_float32`` (the output
+    projection's result stays 32-bit, for an arrangement that norms it before it joins the stream)."""
 
     def __init__(self, params, env: BuildEnv, prefix=""):
         super().__init__(params, env, prefix)
@@ -48,6 +49,7 @@ class GQAttention(Mixer):
         self.scale = float(p.get("scale", 1.0 / math.sqrt(self.D)))
         self.bias = bool(p.get("bias", False))
         self.bias_suffix = p.get("bias_suffix")
+        self.out_float32 = bool(p.get("out_float32", False))     # the output projection's result stays 32-bit
         self.Dv = int(p.get("v_dim", self.D))
         self.sink = bool(p.get("sink", False))
         self.norm_after = p.get("qk_norm_order", "before") == "after"
@@ -151,7 +153,7 @@ class GQAttention(Mixer):
         self.attend(qkv[:, :H * D], out, cache.kv, g, ctx)
         if sink is not None:                               # (residual, the norm behind this mixer)
             return self.o.into_residual(out, sink[0], sink[1])
-        return self.o(out)
+        return self.o(out, out_dtype=torch.float32 if self.out_float32 else None)
 
     def attend(self, q, out, kv, g, ctx: StepContext) -> None:
         """Tensor-core kernels where they take the head size (bfloat16; 32, 64, 128), else the

@@ -41,7 +41,9 @@ class GatedDelta(Mixer):
     ("head" or "channel"), ``gate`` ("silu" or "sigmoid"), ``decay_rank`` / ``gate_rank`` (the thin middle of the
     decay's / gate's projection; 0: one matrix; -1: whatever the file holds), and the tensor names ``q_proj``,
     ``k_proj``, ``v_proj`` (their convolutions: the name + ``conv_suffix``), ``beta_proj``, ``A_log``, ``dt_bias``,
-    ``norm``, ``o_proj``, ``decay_proj`` / ``gate_proj`` (with a thin middle: the names of the two matrices as a pair)."""
+    ``norm``, ``o_proj``, ``decay_proj`` / ``gate_proj`` (with a thin middle: the names of the two matrices as a pair).
+    ``out_float32``: the output projection's result stays 32-bit (for an arrangement that norms it before it joins the
+    stream)."""
 
     graph_capturable = True
 
@@ -56,6 +58,7 @@ class GatedDelta(Mixer):
         self.per_channel = p.get("decay", "head") == "channel"
         self.sigmoid_gate = p.get("gate", "silu") == "sigmoid"
         self.decay_rank, self.gate_rank = int(p.get("decay_rank", 0)), int(p.get("gate_rank", 0))
+        self.out_float32 = bool(p.get("out_float32", False))
         if p.get("decay", "head") not in ("head", "channel") or p.get("gate", "silu") not in ("silu", "sigmoid"):
             raise ValueError("gated_delta: decay is head or channel, gate is silu or sigmoid")
         if self.H % self.G or min(self.H, self.G, self.dk, self.dv, self.taps) <= 0:
@@ -123,13 +126,15 @@ class GatedDelta(Mixer):
     def kernel_libraries(self):
         libs = ["delta_rule"] + self.proj.kernel_libraries() + self.o.kernel_libraries()
         for l in (self.decay_up, self.gate_up):
-            if l is not None:
-                libs += l.kernel_libraries()
+            if l is not None:                               # their input is the 32-bit stacked product: the 32-bit product
+                libs += l.kernel_libraries() + ["gemm_f32"]
         return libs
 
     def forward(self, x, ctx: StepContext, cache: CacheBinding):
         T = x.shape[0]
-        P = self.proj(x)
+        # the stacked product's result stays 32-bit: what enters the recurrence is then rounded nowhere behind x itself
+        # (its columns feed convolutions, unit norms and exponentials, where a bfloat16 rounding travels far)
+        P = self.proj(x, out_dtype=torch.float32)
         cq, ck, cv, cb, ca, cg = self.col
         A = P[:, ca:ca + self.width[4]]
         if self.decay_up is not None:
@@ -146,4 +151,4 @@ class GatedDelta(Mixer):
         o = delta_ops.recurrence(q, k, v, beta, decay, state, ctx.cu_seqlens, slots, fresh, self.per_channel)
         y = torch.empty((T, self.nv), dtype=x.dtype, device=x.device)
         delta_ops.post(o, self.norm_w, gate, self.eps, self.sigmoid_gate, y)
-        return self.o(y)
+        return self.o(y, out_dtype=torch.float32 if self.out_float32 else None)
